@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the Jetfire INT8 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload linear|nonlinear]
+
+Default workload ("linear"): one per-block (32x32) INT8 linear layer at the headline GEMM shape M = N = K = 8192 --
+forward Y = X W^T, input gradient dX = dY W (stochastic rounding) and weight gradient dW = dY^T X -- i.e. three GEMM
+launches per step on seeded synthetic operands (int8 uniform in [-127,127], fp16 scales uniform in [1e-3,1e-1]).
+With N > 1 ranks every rank runs the layer on its own batch (weak scaling) and dW is summed across ranks with one NCCL
+all-reduce per step, which is the data-parallel exchange of the training recipe.
+
+One JSON line is printed by rank 0.  `value` is whole-job INT8 tensor throughput (10^12 ops/s) with operands resident in
+HBM; `e2e` is the same metric through the public Python API with HOST (pinned) operands and results, copies inside the
+timed region; `roofline` describes the forward GEMM kernel; `cpu_baseline` is the CPU oracle on a bounded sample.
+`--impl reference` times the reference algorithm's CPU restatement (oracle/) on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "per-block INT8 GEMM TOPS"
+UNIT = "TOPS"
+
+
+# ------------------------------------------------------------------------------------------------ helpers
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ts, line in self.lines:
+            if ts < t0 - 0.05 or ts > t1 + 0.15:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:   # region shorter than a sampling period: fall back to every sample taken
+            for ts, line in self.lines:
+                f = [x.strip() for x in line.split(",")]
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except Exception:
+                    pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def gemm_ops(M, N, K):
+    return 2.0 * M * N * K
+
+
+# ------------------------------------------------------------------------------------------------ CPU side (oracle)
+def cpu_linear_sample(O, Ms, Ns, Ks, reps=1):
+    """fwd + dgrad + wgrad of one [Ms x Ns x Ks] layer through the CPU oracle; returns (seconds, ops)."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    X = rng.integers(-127, 128, (Ms, Ks), dtype=np.int8)
+    W = rng.integers(-127, 128, (Ns, Ks), dtype=np.int8)
+    G = rng.integers(-127, 128, (Ms, Ns), dtype=np.int8)
+    SX = rng.uniform(1e-3, 1e-1, (Ms // 32, Ks // 32)).astype(np.float16)
+    SW = rng.uniform(1e-3, 1e-1, (Ns // 32, Ks // 32)).astype(np.float16)
+    SG = rng.uniform(1e-3, 1e-1, (Ms // 32, Ns // 32)).astype(np.float16)
+    noise = O.sr_noise(Ms, Ks, 0, 0)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        O.linear_forward(X, SX, W, SW)
+        O.linear_dgrad(G, SG, W, SW, noise)
+        O.linear_wgrad(G, SG, X, SX)
+    dt = time.perf_counter() - t0
+    return dt, reps * 3 * gemm_ops(Ms, Ns, Ks)
+
+
+def run_reference_arm(args):
+    """The reference algorithm on the host cores (CPU restatement in oracle/; the reference's GEMMs are CUDA-only and its
+    WMMA kernels are the thing being replaced).  Each step is a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import jetfire_oracle as O
+    O.build_c_oracle()
+    cores = len(os.sched_getaffinity(0))
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    Ms, Ns, Ks = 512, 512, 8192
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_linear_sample(O, 256, 256, 1024)
+    tot_t, tot_ops = 0.0, 0.0
+    for _ in range(args.steps):
+        dt, ops = cpu_linear_sample(O, Ms, Ns, Ks)
+        tot_t += dt; tot_ops += ops
+    val = tot_ops / tot_t / 1e12
+    sample = f"fwd+dgrad+wgrad of a {Ms}x{Ns}x{Ks} slice of the 8192^3 layer per step"
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * tot_t / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME, "sample": sample},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+WORKLOAD_NAME = ("per-block INT8 linear layer, M=N=K=8192, block 32x32: forward + dgrad (stochastic rounding) + wgrad GEMMs "
+                 "(GEMM sweep headline shape); dW all-reduced over NCCL when n_gpus > 1")
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from jetfire_int8training_b200 import Linear, Nonlinear, rng
+    from jetfire_int8training_b200._lib import lib
+    L = lib()
+    rng.manual_seed(1234 + rank)
+
+    M = N = K = args.size
+    g = torch.Generator(device=dev).manual_seed(rank)
+    X8 = torch.randint(-127, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+    W8 = torch.randint(-127, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    G8 = torch.randint(-127, 128, (M, N), generator=g, device=dev, dtype=torch.int8)
+
+    def scales(r, c):
+        return (torch.rand(r, c, generator=g, device=dev) * 0.099 + 1e-3).half()
+    SX, SW, SG = scales(M // 32, K // 32), scales(N // 32, K // 32), scales(M // 32, N // 32)
+
+    launches_per_step = 3 + (1 if L.jf_igemm_wgrad_plan(N, K, M, 0) > 1 else 0)
+    fwd_ev = []
+
+    def step(time_fwd=False):
+        if time_fwd:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        y8, sy = Linear.int8_linear_forward(X8, SX, W8, SW, True, 32)
+        if time_fwd:
+            e1.record(); fwd_ev.append((e0, e1))
+        gx8, gsx, gw = Linear.int8_linear_backward(X8, SX, G8, SG, None, W8, SW, 32, stochastic=True)
+        if world > 1:
+            dist.all_reduce(gw)
+        return y8, sy, gx8, gsx, gw
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    torch.cuda.synchronize()
+    t_wall0 = time.time()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step(time_fwd=True)
+    ev1.record()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    if world > 1:
+        dist.barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    err = L.jf_igemm_error_flag()
+
+    ops_step = 3 * gemm_ops(M, N, K)
+    value = world * ops_step * args.steps / (ms * 1e-3) / 1e12
+    fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_ev) / len(fwd_ev)
+
+    # ---------------- end to end through the public API with host buffers
+    host_in = [t.cpu().pin_memory() for t in (X8, SX, W8, SW, G8, SG)]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    outs = step()
+    host_out = [torch.empty_like(o, device="cpu").pin_memory() for o in outs]
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step():
+        x8, sx, w8, sw, g8, sg = [t.to(dev, non_blocking=True) for t in host_in]
+        y8, sy = Linear.int8_linear_forward(x8, sx, w8, sw, True, 32)
+        gx8, gsx, gw = Linear.int8_linear_backward(x8, sx, g8, sg, None, w8, sw, 32, stochastic=True)
+        if world > 1:
+            dist.all_reduce(gw)
+        for h, o in zip(host_out, (y8, sy, gx8, gsx, gw)):
+            h.copy_(o, non_blocking=True)
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step(); e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    e2e_ms = a.elapsed_time(b)
+    if world > 1:
+        tms = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tms.item())
+    e2e_val = world * ops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks = read_peaks()
+        # dense INT8 tensor peak: no measured entry exists; use 2x the measured sustained bf16 cuBLAS rate (INT8 is nominally
+        # 2x bf16 on this part) for a kernel timed inside a long step, and also report against the 4.5e15 nominal.
+        peak_tops = 2.0 * peaks["bf16_tflops_sustained"]
+        fwd_tops = gemm_ops(M, N, K) / (fwd_ms * 1e-3) / 1e12
+        int_mm_tops = None
+        try:
+            a8 = torch.randint(-127, 128, (8192, 8192), device=dev, dtype=torch.int8)
+            b8 = torch.randint(-127, 128, (8192, 8192), device=dev, dtype=torch.int8).t()
+            for _ in range(3):
+                torch._int_mm(a8, b8)
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(10):
+                torch._int_mm(a8, b8)
+            s1.record(); torch.cuda.synchronize()
+            int_mm_tops = gemm_ops(8192, 8192, 8192) * 10 / (s0.elapsed_time(s1) * 1e-3) / 1e12
+        except Exception:
+            pass
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import jetfire_oracle as O
+            O.build_c_oracle()
+            cores = len(os.sched_getaffinity(0))
+            cpu_linear_sample(O, 128, 128, 1024)
+            dt, ops = cpu_linear_sample(O, 512, 512, 8192)
+            cpu = {"value": ops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+                   "sample": "fwd+dgrad+wgrad of a 512x512x8192 slice of the layer, CPU oracle (C, OpenMP), once"}
+        ws_mb = (3 * M * K + 2 * M * N + 2 * M * N) / 2 ** 20
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+                "data": "synthetic",
+                "config": {"workload": WORKLOAD_NAME, "M": M, "N": N, "K": K,
+                           "l2": f"operands+results per step ~{ws_mb:.0f} MiB, larger than the 126 MB L2"},
+                "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": e2e_ms / e2e_steps},
+                "gpu_launches": launches_per_step * args.steps,
+                "clocks": clocks,
+                "roofline": {"bound": "tensor", "kernel": "gemm_kernel<K-major,K-major> (forward)", "achieved": fwd_tops,
+                             "peak": peak_tops, "unit": "TOPS", "frac": fwd_tops / peak_tops,
+                             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
+                             "frac_of_nominal_4500": fwd_tops / 4500.0, "cublas_int_mm_tops": int_mm_tops,
+                             "avg_launch_ms": fwd_ms, "traffic": None},
+                "cpu_baseline": cpu, "gemm_error_flag": err}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_nonlinear(args):
+    """Secondary workload: the nonlinear operator set on [8192,768] and [8192,3072]; prints one JSON line with GB/s per op."""
+    import torch
+    from jetfire_int8training_b200 import Nonlinear as NL
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peaks = read_peaks()
+    res = {}
+    for (M, N) in ((8192, 768), (8192, 3072)):
+        copies = max(4, int(300e6 // (M * N)) + 1)   # rotate through > 256 MB of int8 payload so L2 cannot serve the reads
+        g = torch.Generator(device=dev).manual_seed(0)
+        xs = [torch.randn(M, N, generator=g, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        xf = [x.float() for x in xs[:max(4, copies // 4)]]
+        qs = [NL.int8_quantize(x, 32) for x in xs]
+        gs = [NL.int8_quantize(x * 1e-2, 32) for x in xs]
+        gamma = 1 + 0.1 * torch.randn(N, generator=g, device=dev)
+        mean = torch.zeros(M, device=dev); rstd = torch.ones(M, device=dev)
+        ops = {
+            "quantize_bf16": (lambda i: NL.int8_quantize(xs[i % copies], 32), 3.0),
+            "quantize_bf16_sr": (lambda i: NL.int8_quantize(xs[i % copies], 32, stochastic=True), 3.0),
+            "quantize_transpose_bf16": (lambda i: NL.int8_quantize_transpose(xs[i % copies], 32), 4.0),
+            "transpose": (lambda i: NL.int8_transpose(qs[i % copies][0]), 2.0),
+            "dequantize": (lambda i: NL.int8_dequantize(*qs[i % copies], 32), 5.0),
+            "gelu_fwd": (lambda i: NL.int8_gelu_forward(*qs[i % copies], 32), 2.0),
+            "gelu_bwd_sr": (lambda i: NL.int8_gelu_backward(*qs[i % copies], *gs[i % copies], 32, stochastic=True), 3.0),
+            "ln_fwd": (lambda i: NL.int8_layernorm_forward(*qs[i % copies], gamma, mean, rstd, 32), 2.0),
+            "ln_bwd_sr": (lambda i: NL.int8_layernorm_backward(*qs[i % copies], *gs[i % copies], gamma, 32, mean, rstd, stochastic=True), 3.0),
+            "add_bf16_sr": (lambda i: NL.int8_add_Ifp_Ig16_Ofp_Og(xs[i % copies], *qs[(i + 1) % copies], 32, stochastic=True), 8.0),
+            "add_meanvar_f32": (lambda i: NL.int8_add_Ifp_Ig16_Ofp_Og_MeanVar(xf[i % len(xf)], *qs[i % copies], 32), 10.0),
+        }
+        for name, (fn, bpe) in ops.items():
+            for i in range(args.warmup):
+                fn(i)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            iters = max(args.steps, copies)
+            a.record()
+            for i in range(iters):
+                fn(i)
+            b.record(); torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / iters
+            gbs = bpe * M * N / (ms * 1e-3) / 1e9
+            res[f"{name}[{M}x{N}]"] = {"ms": round(ms, 5), "GBps": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 3),
+                                       "bytes_per_elt": bpe}
+    print(json.dumps({"metric": "nonlinear operator GB/s (algorithmic bytes)", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm_gbs"],
+                      "peak_source": peaks["source"], "note": "timings include the Python wrapper's output allocation", "ops": res}),
+          flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear"])
+    ap.add_argument("--size", type=int, default=8192, help="M = N = K of the linear workload")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    elif args.workload == "nonlinear":
+        run_nonlinear(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

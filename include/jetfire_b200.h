@@ -1,0 +1,166 @@
+/*
+ * jetfire_b200 — C ABI of the B200 (sm_100a) implementation of the Jetfire INT8 data-flow hot path.
+ *
+ * One entry point per kernel of the reference's operator layer.  The reference has no C ABI: its boundary
+ * is a set of Python callables (Jetfire/Nonlinear/*.py, Jetfire/Linear/*.py) and a pybind module
+ * (JetfireGEMMKernel/BlockQuantize/cpp_extension/bindings.cpp:6-35).  Each declaration below cites the
+ * reference callable it stands behind.
+ *
+ * Conventions
+ *   - all pointers are DEVICE pointers unless stated otherwise; payloads are int8 [M,N] row-major, scales are
+ *     IEEE fp16 [M/32, N/32] row-major holding (block absmax)/127; the quantisation block is 32x32;
+ *   - M and N (and K) must be positive multiples of 32; payload pointers must be 16-byte aligned;
+ *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream),
+ *     allocates nothing, never synchronises, and returns 0 on success or a negative jf_status;
+ *   - stochastic rounding uses a counter-based Philox4x32-10 keyed by (seed, offset): element e = row*N+col
+ *     takes word e%4 of the block with counter (e/4, offset); passing a non-NULL `noise` (fp32 [M,N], values in
+ *     [-0.5,0.5)) overrides the generator (used to reproduce the reference bit for bit in tests).
+ */
+#ifndef JETFIRE_B200_H
+#define JETFIRE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    JF_OK = 0,
+    JF_ERR_NULL = -1,        /* a required pointer is NULL */
+    JF_ERR_SHAPE = -2,       /* a dimension is not a positive multiple of 32 (or exceeds a documented limit) */
+    JF_ERR_ALIGN = -3,       /* a pointer or leading dimension breaks the 16-byte alignment rule */
+    JF_ERR_DTYPE = -4,       /* unknown dtype code */
+    JF_ERR_LAUNCH = -5,      /* the CUDA runtime reported a launch error (see jf_last_cuda_error) */
+    JF_ERR_UNSUPPORTED = -6, /* the device is not sm_100 or a needed driver entry point is missing */
+    JF_ERR_ARG = -7          /* any other invalid argument */
+} jf_status;
+
+typedef enum { JF_F32 = 0, JF_F16 = 1, JF_BF16 = 2 } jf_dtype;
+
+/* Text for a status code, and the last CUDA error code seen by this library on the calling thread. */
+const char* jf_status_string(int status);
+int jf_last_cuda_error(void);
+/* ABI version of this header (bumped on any signature change). */
+int jf_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Nonlinear operators (reference: Triton kernels in Jetfire/Nonlinear)
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* int8_quantize(x, QB, stochastic)            Jetfire/Nonlinear/quantize.py:128-164 (kernel :33-117)
+ * int8_quantize_transpose(x, QB, stochastic)  Jetfire/Nonlinear/quantize_transpose.py:131-171 (kernel :33-129)
+ * x: [M,N] of x_dtype.  q: int8 [M,N], s: fp16 [M/32,N/32].  qt (optional, may be NULL): int8 [N,M] = q^T. */
+int jf_int8_quantize(const void* x, int x_dtype, int64_t M, int64_t N, int8_t* q, void* s, int8_t* qt,
+                     int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream);
+
+/* int8_dequantize(x, s_x, QB)                 Jetfire/Nonlinear/dequantize.py:86-116 (kernel :28-84)
+ * y: fp32 [M,N] = fp32(fp16(q) * s)  (the product is rounded to fp16 first, as the reference does). */
+int jf_int8_dequantize(const int8_t* q, const void* s, int64_t M, int64_t N, float* y, void* stream);
+
+/* int8_transpose(x)                           Jetfire/Nonlinear/transpose.py:69-97 (kernel :29-67)
+ * y: int8 [N,M]. */
+int jf_int8_transpose(const int8_t* x, int64_t M, int64_t N, int8_t* y, void* stream);
+
+/* int8_gelu_forward(x, s_x, QB)               Jetfire/Nonlinear/gelu_fwd.py:128-162 (kernel :34-126) */
+int jf_int8_gelu_forward(const int8_t* qx, const void* sx, int64_t M, int64_t N, int8_t* qy, void* sy, void* stream);
+
+/* int8_gelu_backward(x, s_x, g, s_g, QB, stochastic)   Jetfire/Nonlinear/gelu_bwd.py:173-215 (kernel :28-171) */
+int jf_int8_gelu_backward(const int8_t* qx, const void* sx, const int8_t* qg, const void* sg, int64_t M, int64_t N,
+                          int8_t* qd, void* sd, int stochastic, const float* noise, uint64_t seed, uint64_t offset,
+                          void* stream);
+
+/* int8_layernorm_forward(x, sx, weight, mean, rstd, QB, eps)   Jetfire/Nonlinear/layernorm.py:430-465 (kernel :74-190)
+ * gamma fp32 [N]; mean, rstd fp32 [M] are INPUTS (the reference takes the statistics from the caller, has no bias
+ * and ignores eps). */
+int jf_int8_layernorm_forward(const int8_t* qx, const void* sx, const float* gamma, const float* mean, const float* rstd,
+                              int64_t M, int64_t N, int8_t* qy, void* sy, void* stream);
+
+/* int8_layernorm_backward(x, sx, g, sg, w, QB, m, v, stochastic, eps)   Jetfire/Nonlinear/layernorm.py:467-526
+ * (kernels :197-402 and :404-428).  qd/sd: quantised dx; dgamma: fp32 [N].
+ * slab: width of the column slab over which the two row reductions of dx are taken; the reference uses 128
+ * (its tile width) although it divides by N; pass 128 for reference behaviour.  N must be a multiple of slab.
+ * scratch: fp32 [(M/32) * N] workspace for the per-32-row partial sums of dgamma (contents on return unspecified). */
+int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* qg, const void* sg, const float* gamma,
+                               const float* mean, const float* rstd, int64_t M, int64_t N, int slab, int8_t* qd, void* sd,
+                               float* dgamma, float* scratch, int stochastic, const float* noise, uint64_t seed,
+                               uint64_t offset, void* stream);
+
+/* int8_add_Ifp_Ig16_Ofp_Og(x1, x2, s_x2, QB, stochastic)   Jetfire/Nonlinear/add.py:164-211 (kernel :29-162)
+ * x1: [M,N] of x1_dtype (fp32 or bf16/fp16 residual).  y1: fp32 [M,N] = x1 + q2*s2.  qy/sy: block-quantised y1;
+ * the reference converts the quotient to int8 by truncation toward zero, and so does this. */
+int jf_int8_add(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1,
+                int8_t* qy, void* sy, int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream);
+
+/* int8_add_Ifp_Ig16_Ofp_Og_MeanVar(x1, x2, s_x2, QB)   Jetfire/Nonlinear/add_mean_var.py:179-231 (kernel :28-177)
+ * As jf_int8_add without stochastic rounding, plus mean[M] and rstd[M] = 1/sqrt(E[y^2]-mean^2) of the fp32 sum.
+ * scratch: fp32 [2 * M * ceil(N/128)] workspace for the per-tile row partial sums. */
+int jf_int8_add_meanvar(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1,
+                        int8_t* qy, void* sy, float* mean, float* rstd, float* scratch, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Per-block INT8 GEMMs (reference: JetfireGEMMKernel/BlockQuantize/cpp_extension, called from Jetfire/Linear)
+ *
+ * All three compute, for each 32-wide K block p in ascending order,
+ *     I_p = A_blk x B_blk^T (int32),   acc = fma(sa[i,p]*sb[j,p], (float)I_p, acc)   (fp32)
+ * and differ in operand layout and epilogue.  Scale tensors are addressed with explicit element strides so both the
+ * natural [rows/32, cols/32] layout and the transposed copies the reference passes are accepted without a copy.
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* Output selector of the re-quantising GEMMs. */
+typedef enum {
+    JF_OUT_INT8 = 0,     /* int8 payload + fp16 scales                                                          */
+    JF_OUT_DEQUANT_F16 = 1 /* fp16 [M,N] = fp16(q) * scale: the torch dequantisation of linear_fwd.py:30 / linear_bwd.py:27 */
+} jf_gemm_out;
+
+/* Forward  Y[M,N] = X[M,K] * W[N,K]^T.
+ * igemm_output_int_quantize_bias_rowcol(X, Wt, bias, biasmax, SXt, SWt, M, N, K)
+ *   JetfireGEMMKernel/BlockQuantize/cpp_extension/igemm/igemm_BlockSquare32OutputIntQuantizeBiasRowCol.cu:386-434
+ *   (kernel :20-383), called from Jetfire/Linear/linear_fwd.py:23 with bias = 0.
+ * sx(i,p) = sx[i*sx_stride_m + p*sx_stride_k], sw(j,p) = sw[j*sw_stride_n + p*sw_stride_k] (fp16).
+ * out_mode JF_OUT_INT8: y8 int8 [M,N] and sy fp16 [M/32,N/32];  JF_OUT_DEQUANT_F16: y16 fp16 [M,N] (y8/sy may be NULL). */
+int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t sx_stride_m, int64_t sx_stride_k,
+                     const void* sw, int64_t sw_stride_n, int64_t sw_stride_k, int64_t M, int64_t N, int64_t K,
+                     int out_mode, int8_t* y8, void* sy, void* y16, void* stream);
+
+/* Input gradient  dX[M,N] = dY[M,K] * W[K,N]   (K = out features, N = in features; W is read in place, no transpose).
+ * igemm_output_int_quantize_stochastic(X, W, SXt, SW, M, N, K)
+ *   .../igemm/igemm_BlockSquare32OutputIntQuantizeStochastic.cu:372-419 (kernel :18-369), from Jetfire/Linear/linear_bwd.py:17.
+ * sg(i,p) = sg[i*sg_stride_m + p*sg_stride_k];  sw(p,j) = sw[p*sw_stride_k + j*sw_stride_n].
+ * stochastic != 0: q = clamp(rint(127*acc/amax + noise), -127, 127) with the Philox noise described above. */
+int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_stride_m, int64_t sg_stride_k,
+                   const void* sw, int64_t sw_stride_k, int64_t sw_stride_n, int64_t M, int64_t N, int64_t K,
+                   int out_mode, int8_t* dx8, void* sdx, void* dx16, int stochastic, const float* noise, uint64_t seed,
+                   uint64_t offset, void* stream);
+
+/* Weight gradient  dW[M,N] = dY^T * X   (K = tokens, M = out features, N = in features).
+ * igemm_output_fp_no_quantize(X, W, SXt, SW, M, N, K)
+ *   .../igemm/igemm_BlockSquare32OutputFp.cu:340-382 (kernel :16-337), from Jetfire/Linear/linear_bwd.py:19.
+ * g_transposed = 0: g is dY itself, int8 [K, M] row-major, read in place (no materialised transpose);
+ * g_transposed = 1: g is the materialised dY^T, int8 [M, K] row-major, as the reference passes it.
+ * x is int8 [K, N] row-major in both cases.
+ * sg(p,i) = sg[p*sg_stride_k + i*sg_stride_m];  sx(p,j) = sx[p*sx_stride_k + j*sx_stride_n].
+ * out_dtype: JF_F16 (reference) or JF_F32.  split_k >= 1: the K blocks are cut into contiguous ranges of
+ * ceil(nblocks/split_k) blocks, each accumulated from zero and summed in ascending order (deterministic);
+ * split_k = 1 reproduces the reference's single sequential accumulation; split_k = 0 lets the library choose.
+ * scratch: fp32 [splits * M * N] workspace, required when the effective split (jf_igemm_wgrad_plan) is > 1. */
+int jf_igemm_wgrad(const int8_t* g, int g_transposed, const int8_t* x, const void* sg, int64_t sg_stride_k,
+                   int64_t sg_stride_m, const void* sx, int64_t sx_stride_k, int64_t sx_stride_n, int64_t M, int64_t N,
+                   int64_t K, int out_dtype, void* dw, int split_k, float* scratch, void* stream);
+
+/* Effective split-K the library would use for (M,N,K,split_k) on the current device (>= 1), so that the caller can
+ * size `scratch`.  Host-only; launches nothing. */
+int jf_igemm_wgrad_plan(int64_t M, int64_t N, int64_t K, int split_k);
+
+/* Plain int8 x int8 -> int32 product C[M,N] = A[M,K] * B[N,K]^T (test/diagnostic entry point).
+ * igemm_basic_int8_gemm   .../igemm/igemm_BasicInt8Gemm.cu:14-110. */
+int jf_igemm_int32(const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c, void* stream);
+
+/* Reads and clears the device-side flag raised when a bounded wait inside a GEMM kernel expired (0 = none).
+ * Diagnostic; synchronises the device.  No counterpart in the reference. */
+int jf_igemm_error_flag(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JETFIRE_B200_H */

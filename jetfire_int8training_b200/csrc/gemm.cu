@@ -1,0 +1,588 @@
+// Per-block (32x32) quantised INT8 GEMMs for sm_100a: forward Y = X W^T, input gradient dX = dY W and weight gradient
+// dW = dY^T X, all from one persistent, warp-specialised kernel.
+//
+// Algorithm (fixed by the reference and its oracle): for every 32-wide K block p, in ascending order,
+//     I_p = A_blk x B_blk^T  (exact int32),      acc = fma(sa[i,p] * sb[j,p], float(I_p), acc)   (fp32)
+// followed by a per-32x32-block re-quantisation (or a dense fp16/fp32 store) of acc.
+//
+// Mapping to the hardware
+//   * CTA tile 128 x 128, one CTA per SM, persistent over a static list of (tile, K-split) work items.
+//   * warp 8 (one lane): TMA producer.  A 128-byte-swizzled 128 x 128 B box per operand per stage = four K blocks;
+//     a 4-stage mbarrier ring (128 KB of shared memory).
+//   * warp 9 (one lane): MMA issuer.  tcgen05.mma kind::i8 has K = 32 = one quantisation block, so every K block is ONE
+//     128x128x32 MMA with accumulation disabled, written to one of four 128-column TMEM accumulators (512 columns);
+//     tcgen05.commit signals the accumulator's "full" barrier and, after the last MMA of a stage, the stage's "empty" one.
+//   * warps 0-7: consumers.  Warp w reads TMEM lanes 32*(w%4).. (rows) and columns 64*(w/4).. of the current
+//     accumulator with tcgen05.ld (each thread: one row, 64 columns = two quantisation blocks), releases it, and does
+//     the int32 -> fp32 conversion and the scale FMA into 64 fp32 registers.  This CUDA-core work, not the tensor
+//     core, bounds the kernel.  Scales are fetched one fp16 per lane for 8 K blocks at a time and broadcast by shuffle.
+//   * operands are consumed in place in either orientation: K-major (row-major [rows, K]) or MN-major (row-major
+//     [K, rows]) through the UMMA descriptor major bits, so no transposed copy of W, dY or X is ever materialised.
+//   * epilogue: a 32x32 block = 32 lanes x 32 thread-local values; absmax is a local max + one redux.sync.
+// Every mbarrier wait is bounded by a clock budget; on expiry the CTA raises an error flag, leaves its loops and
+// frees its tensor memory.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "jf_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace jf {
+
+constexpr int BM = 128, BN = 128;
+constexpr int KB_PER_STAGE = 4;                 // 32-wide K blocks per pipeline stage (128 bytes of K)
+constexpr int STAGES = 4;
+constexpr int STAGE_BYTES = 128 * 128;          // one operand tile
+constexpr int NUM_ACC = 4;                      // TMEM accumulators (128 columns each)
+constexpr int TMEM_COLS = 512;
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = (EPI_WARPS + 2) * 32;
+constexpr int WARP_TMA = EPI_WARPS, WARP_MMA = EPI_WARPS + 1;
+constexpr size_t GEMM_SMEM = 2 * STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
+
+enum GemmMode : int {
+    MODE_INT8 = 0,      // int8 payload + fp16 scales
+    MODE_DEQ16 = 1,     // fp16(q) * scale
+    MODE_F16 = 2,       // dense fp16(acc)
+    MODE_F32 = 3,       // dense fp32 acc (also used for split-K partials)
+    MODE_INT32 = 4      // plain int32 accumulation (diagnostic)
+};
+
+struct GemmParams {
+    int64_t M, N, K;
+    int64_t tiles_m, tiles_n;
+    int64_t nkb;            // K / 32
+    int64_t splits;         // number of K ranges
+    int64_t kb_per_split;   // K blocks per range (last may be shorter)
+    const __half* sa; int64_t sa_sm, sa_sk;   // sa(i,p) = sa[i*sa_sm + p*sa_sk]
+    const __half* sb; int64_t sb_sn, sb_sk;   // sb(j,p) = sb[j*sb_sn + p*sb_sk]
+    int mode;
+    int8_t* out8; __half* out_scale; __half* out16; float* out32; int32_t* out_i32;
+    int stochastic; const float* noise; uint64_t seed, offset;
+};
+
+__device__ int g_gemm_error = 0;   // 0 = ok; otherwise the code of the first wait that expired
+
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
+                *abort_flag = code;
+                atomicCAS(&g_gemm_error, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN, bool INT32ACC>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * STAGES * STAGE_BYTES);
+    uint64_t* full_bar = bars;                       // [STAGES]   TMA -> MMA
+    uint64_t* empty_bar = bars + STAGES;             // [STAGES]   MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;          // [NUM_ACC]  MMA -> consumers
+    uint64_t* acc_empty = bars + 2 * STAGES + NUM_ACC;   // [NUM_ACC]  consumers -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NUM_ACC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < NUM_ACC; ++a) { ptx::mbar_init(&acc_full[a], 1); ptx::mbar_init(&acc_empty[a], EPI_WARPS); }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == WARP_MMA) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    if (warp == WARP_TMA && lane == 0) {
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t num_tiles = p.tiles_m * p.tiles_n;
+    const int64_t num_items = num_tiles * p.splits;
+
+    if (warp == WARP_TMA) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t it = 0;   // running stage counter
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const int64_t tile = item % num_tiles, split = item / num_tiles;
+                const int64_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int64_t kb0 = split * p.kb_per_split;
+                const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
+                for (int64_t kb = kb0; kb < kb1; kb += KB_PER_STAGE, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!(ok = bounded_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1))) break;
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+                    const int32_t k_off = (int32_t)(kb * QB);
+                    if (A_MN) ptx::tma_load_2d(smem_a + s * STAGE_BYTES, &map_a, &full_bar[s], (int32_t)(tm * BM), k_off);
+                    else      ptx::tma_load_2d(smem_a + s * STAGE_BYTES, &map_a, &full_bar[s], k_off, (int32_t)(tm * BM));
+                    if (B_MN) ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], (int32_t)(tn * BN), k_off);
+                    else      ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], k_off, (int32_t)(tn * BN));
+                }
+            }
+        }
+    } else if (warp == WARP_MMA) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_i8(BM, BN, A_MN, B_MN);
+            uint32_t it = 0, ai = 0;   // running stage / accumulator counters
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const int64_t split = item / num_tiles;
+                const int64_t kb0 = split * p.kb_per_split;
+                const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
+                for (int64_t kb = kb0; kb < kb1 && ok; kb += KB_PER_STAGE, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!(ok = bounded_wait(&full_bar[s], ph, abort_flag, 2))) break;
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(smem_a + s * STAGE_BYTES);
+                    const uint32_t b_addr = ptx::smem_u32(smem_b + s * STAGE_BYTES);
+                    const int nblk = (int)min((int64_t)KB_PER_STAGE, kb1 - kb);
+                    for (int j = 0; j < nblk; ++j) {
+                        const bool first = (kb + j == kb0), last = (kb + j + 1 == kb1);
+                        const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
+                        if (!INT32ACC || first) {
+                            if (!(ok = bounded_wait(&acc_empty[a], aph ^ 1u, abort_flag, 3))) break;
+                            ptx::tc_fence_after();
+                        }
+                        // K block j of the stage: 32 bytes further along a K-major row, 32 K-rows (4096 B) further in an MN-major tile
+                        const uint64_t da = ptx::make_smem_desc_sw128(a_addr + (A_MN ? j * 4096 : j * 32), A_MN ? 128 * 128 : 16, 1024);
+                        const uint64_t db = ptx::make_smem_desc_sw128(b_addr + (B_MN ? j * 4096 : j * 32), B_MN ? 128 * 128 : 16, 1024);
+                        // the diagnostic int32 mode lets the tensor core accumulate over K; the real modes never do
+                        ptx::umma_i8(tmem_base + a * BN, da, db, idesc, (INT32ACC && !first) ? 1u : 0u);
+                        if (!INT32ACC || last) {
+                            ptx::umma_commit(&acc_full[a]);
+                            ++ai;
+                        }
+                    }
+                    if (ok) ptx::umma_commit(&empty_bar[s]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ consumers (8 warps)
+        const int quad = warp & 3, half_n = warp >> 2;
+        uint32_t ai = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const int64_t tile = item % num_tiles, split = item / num_tiles;
+            const int64_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int64_t kb0 = split * p.kb_per_split;
+            const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
+            const int64_t rowblk = tm * (BM / QB) + quad;
+            const int64_t colblk0 = tn * (BN / QB) + half_n * 2;
+            const bool row_ok = rowblk < p.M / QB;
+            const bool col_ok0 = colblk0 < p.N / QB, col_ok1 = colblk0 + 1 < p.N / QB;
+
+            float acc[64];
+#pragma unroll
+            for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+
+            // lane-distributed scale fetch: lanes 0-7 hold sa for 8 consecutive K blocks, 8-15 sb of column block 0, 16-23 of block 1
+            auto fetch_scales = [&](int64_t p0) -> float {
+                const int which = lane >> 3;
+                const int64_t pp = p0 + (lane & 7);
+                float v = 0.f;
+                if (pp < kb1) {
+                    if (which == 0) { if (row_ok) v = __half2float(__ldg(p.sa + rowblk * p.sa_sm + pp * p.sa_sk)); }
+                    else if (which == 1) { if (col_ok0) v = __half2float(__ldg(p.sb + colblk0 * p.sb_sn + pp * p.sb_sk)); }
+                    else if (which == 2) { if (col_ok1) v = __half2float(__ldg(p.sb + (colblk0 + 1) * p.sb_sn + pp * p.sb_sk)); }
+                }
+                return v;
+            };
+            float sc_next = INT32ACC ? 0.f : fetch_scales(kb0);
+            float sc_cur = 0.f;
+
+            if (INT32ACC) {
+                const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
+                ++ai;
+                if (!(ok = bounded_wait(&acc_full[a], aph, abort_flag, 4))) break;
+                ptx::tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + a * BN + half_n * 64;
+                uint32_t r0[32], r1[32];
+                ptx::tmem_ld_32x32b_x32(taddr, r0);
+                ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+                ptx::tmem_wait_ld();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { acc[j] = __int_as_float((int)r0[j]); acc[32 + j] = __int_as_float((int)r1[j]); }
+            } else {
+                for (int64_t kb = kb0; kb < kb1; ++kb, ++ai) {
+                    const int pi = (int)((kb - kb0) & 7);
+                    if (pi == 0) {
+                        sc_cur = sc_next;
+                        sc_next = fetch_scales(kb + 8);
+                    }
+                    const float sa_v = __shfl_sync(0xffffffffu, sc_cur, pi);
+                    const float s0 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 8 + pi));
+                    const float s1 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 16 + pi));
+                    const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
+                    if (!(ok = bounded_wait(&acc_full[a], aph, abort_flag, 4))) break;
+                    ptx::tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + a * BN + half_n * 64;
+                    uint32_t r0[32], r1[32];
+                    ptx::tmem_ld_32x32b_x32(taddr, r0);
+                    ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+                    ptx::tmem_wait_ld();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = __fmaf_rn(s0, __int2float_rn((int)r0[j]), acc[j]);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[32 + j] = __fmaf_rn(s1, __int2float_rn((int)r1[j]), acc[32 + j]);
+                }
+                if (!ok) break;
+            }
+
+            // ---------------------------------------------------------------- tile epilogue
+            const int64_t row = tm * BM + quad * 32 + lane;
+            if (!row_ok) continue;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const bool col_ok = b == 0 ? col_ok0 : col_ok1;
+                if (!col_ok) continue;   // warp-uniform
+                const int64_t col = (colblk0 + b) * QB;
+                const float* ab = &acc[32 * b];
+                if (p.mode == MODE_INT32) {
+                    int4* dst = reinterpret_cast<int4*>(p.out_i32 + row * p.N + col);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        dst[k] = make_int4(__float_as_int(ab[4 * k]), __float_as_int(ab[4 * k + 1]), __float_as_int(ab[4 * k + 2]),
+                                           __float_as_int(ab[4 * k + 3]));
+                } else if (p.mode == MODE_F32) {
+                    float4* dst = reinterpret_cast<float4*>(p.out32 + (split * p.M + row) * p.N + col);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) dst[k] = make_float4(ab[4 * k], ab[4 * k + 1], ab[4 * k + 2], ab[4 * k + 3]);
+                } else if (p.mode == MODE_F16) {
+                    int4* dst = reinterpret_cast<int4*>(p.out16 + row * p.N + col);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        __half2 h[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) h[u] = __floats2half2_rn(ab[8 * k + 2 * u], ab[8 * k + 2 * u + 1]);
+                        dst[k] = *reinterpret_cast<int4*>(h);
+                    }
+                } else {
+                    float m = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) m = fmaxf(m, fabsf(ab[j]));
+                    const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
+                    const __half sc16 = __float2half_rn(__fdiv_rn(amax, 127.0f));
+                    const Divisor d = make_divisor(amax);
+                    const bool zero = (amax == 0.f);
+                    uint32_t words[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        float nz[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (p.stochastic) {
+                            if (p.noise) {
+                                const float4 n4 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 4 * k));
+                                nz[0] = n4.x; nz[1] = n4.y; nz[2] = n4.z; nz[3] = n4.w;
+                            } else {
+                                philox_noise4((uint64_t)(row * p.N + col + 4 * k), p.seed, p.offset, nz);
+                            }
+                        }
+                        uint32_t bts[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            float v = div_exact(__fmul_rn(127.0f, ab[4 * k + u]), d);
+                            if (p.stochastic) v = __fadd_rn(v, nz[u]);
+                            v = fminf(fmaxf(v, -127.f), 127.f);
+                            bts[u] = rne_byte(v);
+                        }
+                        words[k] = zero ? 0u : pack4(bts[0], bts[1], bts[2], bts[3]);
+                    }
+                    if (p.mode == MODE_INT8) {
+                        int4* dst = reinterpret_cast<int4*>(p.out8 + row * p.N + col);
+                        dst[0] = make_int4(words[0], words[1], words[2], words[3]);
+                        dst[1] = make_int4(words[4], words[5], words[6], words[7]);
+                        if (lane == 0) p.out_scale[rowblk * (p.N / QB) + colblk0 + b] = sc16;
+                    } else {   // MODE_DEQ16
+                        const float scf = __half2float(sc16);
+                        int4* dst = reinterpret_cast<int4*>(p.out16 + row * p.N + col);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            __half h[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) h[u] = deq16(sbyte(words[2 * k + (u >> 2)], u & 3), scf);
+                            dst[k] = *reinterpret_cast<int4*>(h);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == WARP_MMA) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// out[i] = ((p0[i] + p1[i]) + p2[i]) + ...   then converted to the output type
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partials, int64_t splits, int64_t count, OutT* __restrict__ out) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= count) return;
+    float4 a = *reinterpret_cast<const float4*>(partials + i);
+    for (int64_t k = 1; k < splits; ++k) {
+        const float4 b = *reinterpret_cast<const float4*>(partials + k * count + i);
+        a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y); a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
+    }
+    if constexpr (sizeof(OutT) == 4) {
+        *reinterpret_cast<float4*>(out + i) = a;
+    } else {
+        __half2 h[2] = {__floats2half2_rn(a.x, a.y), __floats2half2_rn(a.z, a.w)};
+        *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<uint2*>(h);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// 2-D uint8 tensor [outer, inner] with row pitch `pitch` bytes; box 128 x 128, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t pitch) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return JF_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    const cuuint64_t strides[1] = {(cuuint64_t)pitch};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return JF_ERR_LAUNCH;
+    }
+    return JF_OK;
+}
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+    bool attr_set[4] = {false, false, false, false};
+};
+static DeviceInfo g_dev[64];
+static std::mutex g_dev_mutex;
+
+static int device_info(DeviceInfo** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JF_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_dev[dev];
+    if (d.sm_count == 0) {
+        cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    }
+    *out = &d;
+    return d.cc_major == 10 ? JF_OK : JF_ERR_UNSUPPORTED;
+}
+
+template <bool A_MN, bool B_MN, bool I32>
+static int launch_gemm(int variant, const int8_t* a, const int8_t* b, GemmParams& p, cudaStream_t st) {
+    DeviceInfo* di = nullptr;
+    if (int e = device_info(&di)) return e;
+    auto kern = gemm_kernel<A_MN, B_MN, I32>;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!di->attr_set[variant]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM) != cudaSuccess)
+                return JF_ERR_LAUNCH;
+            di->attr_set[variant] = true;
+        }
+    }
+    CUtensorMap ma, mb;
+    // K-major operand: [rows, K] row-major -> inner = K.  MN-major operand: [K, rows] row-major -> inner = rows.
+    if (int e = A_MN ? make_map(&ma, a, p.M, p.K, p.M) : make_map(&ma, a, p.K, p.M, p.K)) return e;
+    if (int e = B_MN ? make_map(&mb, b, p.N, p.K, p.N) : make_map(&mb, b, p.K, p.N, p.K)) return e;
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.N + BN - 1) / BN;
+    p.nkb = p.K / QB;
+    const int64_t items = p.tiles_m * p.tiles_n * p.splits;
+    const unsigned grid = (unsigned)(items < di->sm_count ? items : di->sm_count);
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, p);
+    return check_launch();
+}
+
+static int plan_splits(int64_t M, int64_t N, int64_t K, int split_k, int sm_count, int64_t* per_out) {
+    const int64_t nkb = K / QB;
+    int64_t s = split_k;
+    if (s <= 0) {
+        const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+        s = sm_count / tiles;
+        const int64_t cap = nkb / 16;   // keep at least 16 K blocks per range
+        if (s > cap) s = cap;
+        if (s < 1) s = 1;
+    }
+    if (s > nkb) s = nkb;
+    const int64_t per = (nkb + s - 1) / s;
+    if (per_out) *per_out = per;
+    return (int)((nkb + per - 1) / per);
+}
+
+}  // namespace jf
+
+using namespace jf;
+
+static inline int check_gemm_dims(int64_t M, int64_t N, int64_t K) {
+    if (!mult32(M) || !mult32(N) || !mult32(K)) return JF_ERR_SHAPE;
+    if (M > (1LL << 30) || N > (1LL << 30) || K > (1LL << 30)) return JF_ERR_SHAPE;
+    return JF_OK;
+}
+
+extern "C" {
+
+int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t sx_stride_m, int64_t sx_stride_k, const void* sw,
+                     int64_t sw_stride_n, int64_t sw_stride_k, int64_t M, int64_t N, int64_t K, int out_mode, int8_t* y8, void* sy,
+                     void* y16, void* stream) {
+    if (!x || !w || !sx || !sw) return JF_ERR_NULL;
+    if (int e = check_gemm_dims(M, N, K)) return e;
+    if (!aligned16(x) || !aligned16(w)) return JF_ERR_ALIGN;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.splits = 1; p.kb_per_split = K / QB;
+    p.sa = (const __half*)sx; p.sa_sm = sx_stride_m; p.sa_sk = sx_stride_k;
+    p.sb = (const __half*)sw; p.sb_sn = sw_stride_n; p.sb_sk = sw_stride_k;
+    if (out_mode == JF_OUT_INT8) {
+        if (!y8 || !sy) return JF_ERR_NULL;
+        if (!aligned16(y8)) return JF_ERR_ALIGN;
+        p.mode = MODE_INT8; p.out8 = y8; p.out_scale = (__half*)sy;
+    } else if (out_mode == JF_OUT_DEQUANT_F16) {
+        if (!y16) return JF_ERR_NULL;
+        if (!aligned16(y16)) return JF_ERR_ALIGN;
+        p.mode = MODE_DEQ16; p.out16 = (__half*)y16;
+    } else {
+        return JF_ERR_ARG;
+    }
+    return launch_gemm<false, false, false>(0, x, w, p, (cudaStream_t)stream);
+}
+
+int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_stride_m, int64_t sg_stride_k, const void* sw,
+                   int64_t sw_stride_k, int64_t sw_stride_n, int64_t M, int64_t N, int64_t K, int out_mode, int8_t* dx8, void* sdx,
+                   void* dx16, int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream) {
+    if (!g || !w || !sg || !sw) return JF_ERR_NULL;
+    if (int e = check_gemm_dims(M, N, K)) return e;
+    if (!aligned16(g) || !aligned16(w) || (noise && !aligned16(noise))) return JF_ERR_ALIGN;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.splits = 1; p.kb_per_split = K / QB;
+    p.sa = (const __half*)sg; p.sa_sm = sg_stride_m; p.sa_sk = sg_stride_k;
+    p.sb = (const __half*)sw; p.sb_sn = sw_stride_n; p.sb_sk = sw_stride_k;
+    p.stochastic = stochastic; p.noise = noise; p.seed = seed; p.offset = offset;
+    if (out_mode == JF_OUT_INT8) {
+        if (!dx8 || !sdx) return JF_ERR_NULL;
+        if (!aligned16(dx8)) return JF_ERR_ALIGN;
+        p.mode = MODE_INT8; p.out8 = dx8; p.out_scale = (__half*)sdx;
+    } else if (out_mode == JF_OUT_DEQUANT_F16) {
+        if (!dx16) return JF_ERR_NULL;
+        if (!aligned16(dx16)) return JF_ERR_ALIGN;
+        p.mode = MODE_DEQ16; p.out16 = (__half*)dx16;
+    } else {
+        return JF_ERR_ARG;
+    }
+    return launch_gemm<false, true, false>(1, g, w, p, (cudaStream_t)stream);
+}
+
+int jf_igemm_wgrad_plan(int64_t M, int64_t N, int64_t K, int split_k) {
+    if (check_gemm_dims(M, N, K)) return JF_ERR_SHAPE;
+    int sm = 148;
+    DeviceInfo* di = nullptr;
+    if (device_info(&di) == JF_OK) sm = di->sm_count;
+    return plan_splits(M, N, K, split_k, sm, nullptr);
+}
+
+int jf_igemm_wgrad(const int8_t* g, int g_transposed, const int8_t* x, const void* sg, int64_t sg_stride_k, int64_t sg_stride_m,
+                   const void* sx, int64_t sx_stride_k, int64_t sx_stride_n, int64_t M, int64_t N, int64_t K, int out_dtype, void* dw,
+                   int split_k, float* scratch, void* stream) {
+    if (!g || !x || !sg || !sx || !dw) return JF_ERR_NULL;
+    if (int e = check_gemm_dims(M, N, K)) return e;
+    if (!aligned16(g) || !aligned16(x) || !aligned16(dw)) return JF_ERR_ALIGN;
+    if (out_dtype != JF_F16 && out_dtype != JF_F32) return JF_ERR_DTYPE;
+    DeviceInfo* di = nullptr;
+    if (int e = device_info(&di)) return e;
+    int64_t per = 0;
+    const int splits = plan_splits(M, N, K, split_k, di->sm_count, &per);
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.splits = splits; p.kb_per_split = per;
+    p.sa = (const __half*)sg; p.sa_sm = sg_stride_m; p.sa_sk = sg_stride_k;
+    p.sb = (const __half*)sx; p.sb_sn = sx_stride_n; p.sb_sk = sx_stride_k;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (splits == 1) {
+        if (out_dtype == JF_F16) { p.mode = MODE_F16; p.out16 = (__half*)dw; }
+        else { p.mode = MODE_F32; p.out32 = (float*)dw; }
+        return g_transposed ? launch_gemm<false, true, false>(1, g, x, p, st) : launch_gemm<true, true, false>(2, g, x, p, st);
+    }
+    if (!scratch) return JF_ERR_NULL;
+    if (!aligned16(scratch)) return JF_ERR_ALIGN;
+    p.mode = MODE_F32; p.out32 = scratch;
+    if (int e = g_transposed ? launch_gemm<false, true, false>(1, g, x, p, st) : launch_gemm<true, true, false>(2, g, x, p, st)) return e;
+    const int64_t count = M * N;
+    const unsigned grid = (unsigned)((count / 4 + 255) / 256);
+    if (out_dtype == JF_F16) splitk_reduce_kernel<__half><<<grid, 256, 0, st>>>(scratch, splits, count, (__half*)dw);
+    else splitk_reduce_kernel<float><<<grid, 256, 0, st>>>(scratch, splits, count, (float*)dw);
+    return check_launch();
+}
+
+int jf_igemm_int32(const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c, void* stream) {
+    if (!a || !b || !c) return JF_ERR_NULL;
+    if (int e = check_gemm_dims(M, N, K)) return e;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return JF_ERR_ALIGN;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.splits = 1; p.kb_per_split = K / QB;
+    p.mode = MODE_INT32; p.out_i32 = c;
+    return launch_gemm<false, false, true>(3, a, b, p, (cudaStream_t)stream);
+}
+
+/* Reads (and clears) the device-side error flag raised when a bounded wait inside the GEMM kernel expired.
+ * Synchronises the device.  0 = no error. */
+int jf_igemm_error_flag(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return JF_ERR_LAUNCH;
+    if (v != 0) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+// Shared device helpers for the Jetfire INT8 kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/jetfire_b200.h"
+
+namespace jf {
+
+constexpr int QB = 32;  // quantisation block edge
+
+// ---------------------------------------------------------------------------------------------------------
+// host-side status plumbing
+// ---------------------------------------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+
+inline int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return JF_ERR_LAUNCH;
+    }
+    return JF_OK;
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool mult32(int64_t v) { return v > 0 && (v % 32) == 0; }
+
+// ---------------------------------------------------------------------------------------------------------
+// Philox4x32-10 (Random123).  One call yields the four words of the group g = element_index / 4.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        if (r > 0) {
+            k.x += 0x9E3779B9u;
+            k.y += 0xBB67AE85u;
+        }
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    }
+    return c;
+}
+
+// word -> noise in (-0.5, 0.5): ((w >> 9) - 2^22 + 0.5) * 2^-23, exact in fp32.
+__device__ __forceinline__ float word_to_noise(uint32_t w) {
+    const int k = (int)(w >> 9) - (1 << 22);
+    return __fadd_rn(__fmul_rn((float)k, 1.1920928955078125e-07f), 5.9604644775390625e-08f);
+}
+
+// Noise for the 4 consecutive elements starting at linear index e (e % 4 == 0).
+__device__ __forceinline__ void philox_noise4(uint64_t e, uint64_t seed, uint64_t offset, float out[4]) {
+    const uint64_t g = e >> 2;
+    const uint4 w = philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), (uint32_t)offset, (uint32_t)(offset >> 32)),
+                                  make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    out[0] = word_to_noise(w.x);
+    out[1] = word_to_noise(w.y);
+    out[2] = word_to_noise(w.z);
+    out[3] = word_to_noise(w.w);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Exact IEEE division by a value shared across many elements.
+// With y = RN(1/b) (correctly rounded reciprocal), q0 = RN(a*y), r = a - b*q0 (exact in one FMA) and
+// q = RN(q0 + r*y) is the correctly rounded quotient RN(a/b) (Markstein's correction step), provided nothing
+// under/overflows.  The fast path is taken only for b in [2^-60, 2^60]; otherwise div.rn is used.
+// ---------------------------------------------------------------------------------------------------------
+struct Divisor {
+    float b;     // divisor
+    float inv;   // RN(1/b)
+    bool fast;   // fast path is valid
+};
+__device__ __forceinline__ Divisor make_divisor(float b) {
+    Divisor d;
+    d.b = b;
+    d.inv = __frcp_rn(b);
+    const float ab = fabsf(b);
+    d.fast = (ab >= 8.673617379884035e-19f) && (ab <= 1.152921504606847e18f);
+    return d;
+}
+__device__ __forceinline__ float div_exact(float a, const Divisor& d) {
+    if (d.fast) {
+        const float q0 = __fmul_rn(a, d.inv);
+        const float r = __fmaf_rn(-d.b, q0, a);
+        return __fmaf_rn(r, d.inv, q0);
+    }
+    return __fdiv_rn(a, d.b);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Rounding to int8
+// ---------------------------------------------------------------------------------------------------------
+// Stochastic-rounding pre-step of the reference: sign(v) * clamp(|v| + noise, -128, 127).
+__device__ __forceinline__ float sr_prestep(float v, float noise) {
+    const float mag = fminf(fmaxf(__fadd_rn(fabsf(v), noise), -128.f), 127.f);
+    return (__float_as_uint(v) >> 31) ? -mag : mag;
+}
+// Round-half-even to an integer and keep the low byte (llrint followed by a narrowing cast); |v| < 2^22.
+__device__ __forceinline__ uint32_t rne_byte(float v) { return __float_as_uint(__fadd_rn(v, 12582912.0f)) & 0xFFu; }
+// Truncation toward zero, low byte (a plain float -> int8 cast).
+__device__ __forceinline__ uint32_t trunc_byte(float v) { return ((uint32_t)__float2int_rz(v)) & 0xFFu; }
+
+__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+    return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+
+// fp16 product of an int8 payload value and its fp16 scale, as the reference's "int8 * fp16" does
+// (the int8 is converted to fp16 exactly, the product is rounded to fp16 once).  q*s is exact in fp32.
+__device__ __forceinline__ __half deq16(int q, float s_as_float) { return __float2half_rn(__fmul_rn((float)q, s_as_float)); }
+
+__device__ __forceinline__ int sbyte(uint32_t w, int i) { return (int)(int8_t)(w >> (8 * i)); }
+
+// dtype-generic 16-element row chunk loads -> fp32
+template <typename T>
+struct Load16;
+template <>
+struct Load16<float> {
+    static __device__ __forceinline__ void load(const float* p, float v[16]) {
+        const float4* p4 = reinterpret_cast<const float4*>(p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 t = __ldg(p4 + i);
+            v[4 * i + 0] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    }
+};
+template <>
+struct Load16<__half> {
+    static __device__ __forceinline__ void load(const __half* p, float v[16]) {
+        const uint4* p4 = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 t = __ldg(p4 + i);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                const float2 f = __half22float2(h);
+                v[8 * i + 2 * j] = f.x; v[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+};
+template <>
+struct Load16<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float v[16]) {
+        const uint4* p4 = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 t = __ldg(p4 + i);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+                v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            }
+        }
+    }
+};
+
+}  // namespace jf
