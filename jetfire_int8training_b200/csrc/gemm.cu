@@ -23,6 +23,7 @@
 // frees its tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "jf_common.cuh"
@@ -81,7 +82,59 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     }
 }
 
-template <bool A_MN, bool B_MN, bool INT32ACC>
+
+// ---------------------------------------------------------------------------------------------------------
+// Consumer arithmetic.  acc is kept as packed pairs of fp32 so the scale FMA can use the two-wide fma.rn.f32x2.
+// int32 -> fp32 is exact for |I| <= 32*127^2 < 2^22 in either form:
+//   CONV_I2F  : cvt.rn.f32.s32
+//   CONV_MAGIC: bits(I + 0x4B400000) is the float 1.5*2^23 + I; subtracting 1.5*2^23 (exact) leaves float(I).
+// The integer add runs on the integer pipe, the subtract and the FMA two-wide on the FMA pipe, so the conversion no
+// longer queues on the narrow conversion unit.
+// ---------------------------------------------------------------------------------------------------------
+enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_MAGIC_SCALAR = 2, CONV_MIXED = 3 };
+constexpr int CONV_DEFAULT = CONV_MAGIC;
+
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// acc2[j] (pairs) += s * float(r[2j], r[2j+1]) for the 32 int32 values in r
+template <int CONV>
+__device__ __forceinline__ void scale_accumulate(uint64_t (&acc2)[16], const uint32_t (&r)[32], float s) {
+    const uint64_t s2 = pack2(s, s);
+    const uint64_t negc = pack2(-12582912.0f, -12582912.0f);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool magic = (CONV == CONV_MAGIC) || (CONV == CONV_MAGIC_SCALAR) || (CONV == CONV_MIXED && (j & 1));
+        if (CONV == CONV_MAGIC_SCALAR) {
+            float a0, a1;
+            unpack2(acc2[j], a0, a1);
+            const float x0 = __fadd_rn(__int_as_float((int)r[2 * j] + 0x4B400000), -12582912.0f);
+            const float x1 = __fadd_rn(__int_as_float((int)r[2 * j + 1] + 0x4B400000), -12582912.0f);
+            acc2[j] = pack2(__fmaf_rn(s, x0, a0), __fmaf_rn(s, x1, a1));
+        } else if (magic) {
+            const uint64_t x = add2(pack2(__int_as_float((int)r[2 * j] + 0x4B400000), __int_as_float((int)r[2 * j + 1] + 0x4B400000)), negc);
+            acc2[j] = fma2(s2, x, acc2[j]);
+        } else {
+            acc2[j] = fma2(s2, pack2(__int2float_rn((int)r[2 * j]), __int2float_rn((int)r[2 * j + 1])), acc2[j]);
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN, bool INT32ACC, int CONV>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -195,9 +248,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const bool row_ok = rowblk < p.M / QB;
             const bool col_ok0 = colblk0 < p.N / QB, col_ok1 = colblk0 + 1 < p.N / QB;
 
-            float acc[64];
+            uint64_t acc_lo[16], acc_hi[16];   // fp32 accumulators as packed pairs: columns 0-31 and 32-63 of this thread's row
 #pragma unroll
-            for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+            for (int j = 0; j < 16; ++j) { acc_lo[j] = 0ull; acc_hi[j] = 0ull; }
 
             // lane-distributed scale fetch: lanes 0-7 hold sa for 8 consecutive K blocks, 8-15 sb of column block 0, 16-23 of block 1
             auto fetch_scales = [&](int64_t p0) -> float {
@@ -213,24 +266,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             };
             float sc_next = INT32ACC ? 0.f : fetch_scales(kb0);
             float sc_cur = 0.f;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + half_n * 64;
 
             if (INT32ACC) {
                 const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
                 ++ai;
                 if (!(ok = bounded_wait(&acc_full[a], aph, abort_flag, 4))) break;
                 ptx::tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + a * BN + half_n * 64;
                 uint32_t r0[32], r1[32];
-                ptx::tmem_ld_32x32b_x32(taddr, r0);
-                ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-                ptx::tmem_wait_ld();
+                ptx::tmem_ld_32x32b_x32(lane_base + a * BN, r0);
+                ptx::tmem_ld_32x32b_x32(lane_base + a * BN + 32, r1);
+                ptx::tmem_wait_ld_regs(r0);
+                ptx::tmem_wait_ld_regs(r1);
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) { acc[j] = __int_as_float((int)r0[j]); acc[32 + j] = __int_as_float((int)r1[j]); }
+                for (int j = 0; j < 16; ++j) {
+                    acc_lo[j] = pack2(__int_as_float((int)r0[2 * j]), __int_as_float((int)r0[2 * j + 1]));
+                    acc_hi[j] = pack2(__int_as_float((int)r1[2 * j]), __int_as_float((int)r1[2 * j + 1]));
+                }
             } else {
-                for (int64_t kb = kb0; kb < kb1; ++kb, ++ai) {
+                // Software pipeline over the two 32-column halves: while one half is being converted and accumulated, the
+                // tcgen05.ld of the other half (or of the next K block's first half) is in flight.
+                uint32_t r0[32], r1[32];
+                uint32_t a = ai % NUM_ACC;
+                if (!(ok = bounded_wait(&acc_full[a], (ai / NUM_ACC) & 1u, abort_flag, 4))) break;
+                ptx::tc_fence_after();
+                ptx::tmem_ld_32x32b_x32(lane_base + a * BN, r0);
+                for (int64_t kb = kb0; kb < kb1; ++kb) {
                     const int pi = (int)((kb - kb0) & 7);
                     if (pi == 0) {
                         sc_cur = sc_next;
@@ -239,23 +303,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const float sa_v = __shfl_sync(0xffffffffu, sc_cur, pi);
                     const float s0 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 8 + pi));
                     const float s1 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 16 + pi));
-                    const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
-                    if (!(ok = bounded_wait(&acc_full[a], aph, abort_flag, 4))) break;
-                    ptx::tc_fence_after();
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + a * BN + half_n * 64;
-                    uint32_t r0[32], r1[32];
-                    ptx::tmem_ld_32x32b_x32(taddr, r0);
-                    ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-                    ptx::tmem_wait_ld();
+                    ptx::tmem_wait_ld_regs(r0);
+                    ptx::tmem_ld_32x32b_x32(lane_base + a * BN + 32, r1);
+                    scale_accumulate<CONV>(acc_lo, r0, s0);
+                    ptx::tmem_wait_ld_regs(r1);
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[j] = __fmaf_rn(s0, __int2float_rn((int)r0[j]), acc[j]);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[32 + j] = __fmaf_rn(s1, __int2float_rn((int)r1[j]), acc[32 + j]);
+                    ++ai;
+                    if (kb + 1 < kb1) {
+                        a = ai % NUM_ACC;
+                        if (!(ok = bounded_wait(&acc_full[a], (ai / NUM_ACC) & 1u, abort_flag, 4))) break;
+                        ptx::tc_fence_after();
+                        ptx::tmem_ld_32x32b_x32(lane_base + a * BN, r0);
+                    }
+                    scale_accumulate<CONV>(acc_hi, r1, s1);
                 }
                 if (!ok) break;
+            }
+            float acc[64];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                unpack2(acc_lo[j], acc[2 * j], acc[2 * j + 1]);
+                unpack2(acc_hi[j], acc[32 + 2 * j], acc[32 + 2 * j + 1]);
             }
 
             // ---------------------------------------------------------------- tile epilogue
@@ -405,7 +475,7 @@ static int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t o
 struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
-    bool attr_set[4] = {false, false, false, false};
+    bool attr_set[8] = {false, false, false, false, false, false, false, false};
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
@@ -423,11 +493,11 @@ static int device_info(DeviceInfo** out) {
     return d.cc_major == 10 ? JF_OK : JF_ERR_UNSUPPORTED;
 }
 
-template <bool A_MN, bool B_MN, bool I32>
+template <bool A_MN, bool B_MN, bool I32, int CONV = CONV_DEFAULT>
 static int launch_gemm(int variant, const int8_t* a, const int8_t* b, GemmParams& p, cudaStream_t st) {
     DeviceInfo* di = nullptr;
     if (int e = device_info(&di)) return e;
-    auto kern = gemm_kernel<A_MN, B_MN, I32>;
+    auto kern = gemm_kernel<A_MN, B_MN, I32, CONV>;
     {
         std::lock_guard<std::mutex> lock(g_dev_mutex);
         if (!di->attr_set[variant]) {
@@ -498,7 +568,14 @@ int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t s
     } else {
         return JF_ERR_ARG;
     }
-    return launch_gemm<false, false, false>(0, x, w, p, (cudaStream_t)stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    static const int conv = [] { const char* e = getenv("JF_GEMM_CONV"); return e ? atoi(e) : (int)CONV_DEFAULT; }();
+    switch (conv) {   // tuning switch for the conversion strategy of the forward kernel
+        case CONV_I2F: return launch_gemm<false, false, false, CONV_I2F>(4, x, w, p, st);
+        case CONV_MAGIC_SCALAR: return launch_gemm<false, false, false, CONV_MAGIC_SCALAR>(5, x, w, p, st);
+        case CONV_MIXED: return launch_gemm<false, false, false, CONV_MIXED>(6, x, w, p, st);
+        default: return launch_gemm<false, false, false, CONV_MAGIC>(0, x, w, p, st);
+    }
 }
 
 int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_stride_m, int64_t sg_stride_k, const void* sw,
