@@ -98,6 +98,20 @@ int jf_int8_add(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, 
 int jf_int8_add_meanvar(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1,
                         int8_t* qy, void* sy, float* mean, float* rstd, float* scratch, void* stream);
 
+/* Allocation-free variant of jf_int8_add_meanvar.  It has no counterpart in the reference.
+ * For hosts that cannot hand the library a workspace (a plug-in interface that passes only inputs and outputs, a runtime
+ * with one fixed device arena and no allocator calls after start-up, a loop that must avoid cudaMalloc because it
+ * synchronises the device): the row-partial workspace is a fixed 4 MiB array inside the library image, resident on every
+ * GPU that loads the library until the process exits.  Same arguments and results as jf_int8_add_meanvar minus `scratch`.
+ * Limit: 2 * M * ceil(N/128) <= 1048576 floats; larger shapes return JF_ERR_SHAPE (use jf_int8_add_meanvar instead).
+ * The first call on each device resolves the array's device address (cudaGetSymbolAddress); make that first call
+ * outside any stream capture.  The call itself never calls cudaMalloc/cudaFree or any allocating routine.
+ * All calls on a device share the one array, which keeps the previous call's contents: nothing in it needs to start at
+ * zero (every partial is rewritten before it is read), but two calls whose kernels overlap on the GPU (different streams
+ * without ordering) race on it. */
+int jf_int8_add_meanvar_noalloc(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N,
+                                float* y1, int8_t* qy, void* sy, float* mean, float* rstd, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Per-block INT8 GEMMs (reference: JetfireGEMMKernel/BlockQuantize/cpp_extension, called from Jetfire/Linear)
  *

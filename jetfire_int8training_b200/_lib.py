@@ -26,6 +26,7 @@ SIGNATURES = {
                                     _u64, _u64, _vp], _int),
     "jf_int8_add": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _int, _vp, _u64, _u64, _vp], _int),
     "jf_int8_add_meanvar": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp], _int),
+    "jf_int8_add_meanvar_noalloc": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp], _int),
     "jf_igemm_forward": ([_vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp], _int),
     "jf_igemm_dgrad": ([_vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp,
                         _u64, _u64, _vp], _int),
