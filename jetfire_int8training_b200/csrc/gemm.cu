@@ -7,9 +7,11 @@
 //
 // Mapping to the hardware
 //   * CTA tile 128 x 128, one CTA per SM, persistent over a static list of (tile, K-split) work items.
+//   * 384 threads = two consumer warpgroups + one producer warpgroup; setmaxnreg moves registers from the producer
+//     warpgroup (56 each) to the consumers (224 each) so the conversion/FMA stream has enough independent work in flight.
 //   * warp 8 (one lane): TMA producer.  A 128-byte-swizzled 128 x 128 B box per operand per stage = four K blocks;
 //     a 4-stage mbarrier ring (128 KB of shared memory).
-//   * warp 9 (one lane): MMA issuer.  tcgen05.mma kind::i8 has K = 32 = one quantisation block, so every K block is ONE
+//   * warps 9-10 (one lane each): MMA issuers, alternating K blocks.  tcgen05.mma kind::i8 has K = 32 = one quantisation block, so every K block is ONE
 //     128x128x32 MMA with accumulation disabled, written to one of four 128-column TMEM accumulators (512 columns);
 //     tcgen05.commit signals the accumulator's "full" barrier and, after the last MMA of a stage, the stage's "empty" one.
 //   * warps 0-7: consumers.  Warp w reads TMEM lanes 32*(w%4).. (rows) and columns 64*(w/4).. of the current
@@ -35,11 +37,7 @@ constexpr int BM = 128, BN = 128;
 constexpr int KB_PER_STAGE = 4;                 // 32-wide K blocks per pipeline stage (128 bytes of K)
 constexpr int STAGES = 4;
 constexpr int STAGE_BYTES = 128 * 128;          // one operand tile
-constexpr int NUM_ACC = 4;                      // TMEM accumulators (128 columns each)
 constexpr int TMEM_COLS = 512;
-constexpr int EPI_WARPS = 8;
-constexpr int GEMM_THREADS = (EPI_WARPS + 2) * 32;
-constexpr int WARP_TMA = EPI_WARPS, WARP_MMA = EPI_WARPS + 1;
 constexpr size_t GEMM_SMEM = 2 * STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -66,11 +64,13 @@ struct GemmParams {
 
 __device__ int g_gemm_error = 0;   // 0 = ok; otherwise the code of the first wait that expired
 
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
         if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (BACKOFF) __nanosleep(20);
         if ((it & 255u) == 255u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
@@ -82,17 +82,17 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     }
 }
 
-
 // ---------------------------------------------------------------------------------------------------------
 // Consumer arithmetic.  acc is kept as packed pairs of fp32 so the scale FMA can use the two-wide fma.rn.f32x2.
 // int32 -> fp32 is exact for |I| <= 32*127^2 < 2^22 in either form:
-//   CONV_I2F  : cvt.rn.f32.s32
-//   CONV_MAGIC: bits(I + 0x4B400000) is the float 1.5*2^23 + I; subtracting 1.5*2^23 (exact) leaves float(I).
-// The integer add runs on the integer pipe, the subtract and the FMA two-wide on the FMA pipe, so the conversion no
-// longer queues on the narrow conversion unit.
+//   CONV_I2F  : cvt.rn.f32.s32 (conversion unit)
+//   CONV_MAGIC: bits(I + 0x4B400000) is the float 1.5*2^23 + I; subtracting 1.5*2^23 (exact) leaves float(I)
+//               (integer pipe + FMA pipe)
+//   CONV_MIXED: alternate pairs between the two, to spread the work over three pipes.
+// CONV_INT32 adds the raw integers (diagnostic int32 GEMM); the CONV_PROBE_* modes exist only to time the kernel's
+// data movement without its arithmetic and produce meaningless results.
 // ---------------------------------------------------------------------------------------------------------
-enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_MAGIC_SCALAR = 2, CONV_MIXED = 3 };
-constexpr int CONV_DEFAULT = CONV_MAGIC;
+enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_MIXED = 3, CONV_INT32 = 4, CONV_PROBE_NONE = 5, CONV_PROBE_NOLD = 6 };
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
     uint64_t r;
@@ -114,18 +114,24 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // acc2[j] (pairs) += s * float(r[2j], r[2j+1]) for the 32 int32 values in r
 template <int CONV>
 __device__ __forceinline__ void scale_accumulate(uint64_t (&acc2)[16], const uint32_t (&r)[32], float s) {
+    if (CONV == CONV_INT32) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t lo = (uint32_t)acc2[j] + r[2 * j], hi = (uint32_t)(acc2[j] >> 32) + r[2 * j + 1];
+            acc2[j] = ((uint64_t)hi << 32) | lo;
+        }
+        return;
+    }
+    if (CONV == CONV_PROBE_NONE || CONV == CONV_PROBE_NOLD) {
+        acc2[0] += ((uint64_t)r[1] << 32) | r[0];
+        return;
+    }
     const uint64_t s2 = pack2(s, s);
     const uint64_t negc = pack2(-12582912.0f, -12582912.0f);
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        const bool magic = (CONV == CONV_MAGIC) || (CONV == CONV_MAGIC_SCALAR) || (CONV == CONV_MIXED && (j & 1));
-        if (CONV == CONV_MAGIC_SCALAR) {
-            float a0, a1;
-            unpack2(acc2[j], a0, a1);
-            const float x0 = __fadd_rn(__int_as_float((int)r[2 * j] + 0x4B400000), -12582912.0f);
-            const float x1 = __fadd_rn(__int_as_float((int)r[2 * j + 1] + 0x4B400000), -12582912.0f);
-            acc2[j] = pack2(__fmaf_rn(s, x0, a0), __fmaf_rn(s, x1, a1));
-        } else if (magic) {
+        const bool magic = (CONV == CONV_MAGIC) || (CONV == CONV_MIXED && (j & 1));
+        if (magic) {
             const uint64_t x = add2(pack2(__int_as_float((int)r[2 * j] + 0x4B400000), __int_as_float((int)r[2 * j + 1] + 0x4B400000)), negc);
             acc2[j] = fma2(s2, x, acc2[j]);
         } else {
@@ -134,287 +140,77 @@ __device__ __forceinline__ void scale_accumulate(uint64_t (&acc2)[16], const uin
     }
 }
 
-template <bool A_MN, bool B_MN, bool INT32ACC, int CONV>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + STAGES * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * STAGES * STAGE_BYTES);
-    uint64_t* full_bar = bars;                       // [STAGES]   TMA -> MMA
-    uint64_t* empty_bar = bars + STAGES;             // [STAGES]   MMA -> TMA
-    uint64_t* acc_full = bars + 2 * STAGES;          // [NUM_ACC]  MMA -> consumers
-    uint64_t* acc_empty = bars + 2 * STAGES + NUM_ACC;   // [NUM_ACC]  consumers -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NUM_ACC);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < NUM_ACC; ++a) { ptx::mbar_init(&acc_full[a], 1); ptx::mbar_init(&acc_empty[a], EPI_WARPS); }
-        *abort_flag = 0;
-        ptx::fence_barrier_init();
-    }
-    if (warp == WARP_MMA) {
-        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
-        ptx::tmem_relinquish();
-    }
-    if (warp == WARP_TMA && lane == 0) {
-        ptx::prefetch_tensormap(&map_a);
-        ptx::prefetch_tensormap(&map_b);
-    }
-    ptx::tc_fence_before();
-    __syncthreads();
-    ptx::tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    const int64_t num_tiles = p.tiles_m * p.tiles_n;
-    const int64_t num_items = num_tiles * p.splits;
-
-    if (warp == WARP_TMA) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            uint32_t it = 0;   // running stage counter
-            bool ok = true;
-            for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-                const int64_t tile = item % num_tiles, split = item / num_tiles;
-                const int64_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-                const int64_t kb0 = split * p.kb_per_split;
-                const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
-                for (int64_t kb = kb0; kb < kb1; kb += KB_PER_STAGE, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                    if (!(ok = bounded_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1))) break;
-                    ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
-                    const int32_t k_off = (int32_t)(kb * QB);
-                    if (A_MN) ptx::tma_load_2d(smem_a + s * STAGE_BYTES, &map_a, &full_bar[s], (int32_t)(tm * BM), k_off);
-                    else      ptx::tma_load_2d(smem_a + s * STAGE_BYTES, &map_a, &full_bar[s], k_off, (int32_t)(tm * BM));
-                    if (B_MN) ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], (int32_t)(tn * BN), k_off);
-                    else      ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], k_off, (int32_t)(tn * BN));
-                }
-            }
-        }
-    } else if (warp == WARP_MMA) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_i8(BM, BN, A_MN, B_MN);
-            uint32_t it = 0, ai = 0;   // running stage / accumulator counters
-            bool ok = true;
-            for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-                const int64_t split = item / num_tiles;
-                const int64_t kb0 = split * p.kb_per_split;
-                const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
-                for (int64_t kb = kb0; kb < kb1 && ok; kb += KB_PER_STAGE, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                    if (!(ok = bounded_wait(&full_bar[s], ph, abort_flag, 2))) break;
-                    ptx::tc_fence_after();
-                    const uint32_t a_addr = ptx::smem_u32(smem_a + s * STAGE_BYTES);
-                    const uint32_t b_addr = ptx::smem_u32(smem_b + s * STAGE_BYTES);
-                    const int nblk = (int)min((int64_t)KB_PER_STAGE, kb1 - kb);
-                    for (int j = 0; j < nblk; ++j) {
-                        const bool first = (kb + j == kb0), last = (kb + j + 1 == kb1);
-                        const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
-                        if (!INT32ACC || first) {
-                            if (!(ok = bounded_wait(&acc_empty[a], aph ^ 1u, abort_flag, 3))) break;
-                            ptx::tc_fence_after();
-                        }
-                        // K block j of the stage: 32 bytes further along a K-major row, 32 K-rows (4096 B) further in an MN-major tile
-                        const uint64_t da = ptx::make_smem_desc_sw128(a_addr + (A_MN ? j * 4096 : j * 32), A_MN ? 128 * 128 : 16, 1024);
-                        const uint64_t db = ptx::make_smem_desc_sw128(b_addr + (B_MN ? j * 4096 : j * 32), B_MN ? 128 * 128 : 16, 1024);
-                        // the diagnostic int32 mode lets the tensor core accumulate over K; the real modes never do
-                        ptx::umma_i8(tmem_base + a * BN, da, db, idesc, (INT32ACC && !first) ? 1u : 0u);
-                        if (!INT32ACC || last) {
-                            ptx::umma_commit(&acc_full[a]);
-                            ++ai;
-                        }
-                    }
-                    if (ok) ptx::umma_commit(&empty_bar[s]);
-                }
-            }
+// Re-quantise / convert one 32x32 block held as 32 lanes x 32 values and store it.
+__device__ __forceinline__ void store_block(const GemmParams& p, const float (&ab)[32], int64_t row, int64_t col, int64_t rowblk,
+                                            int64_t colblk, int64_t split, int lane) {
+    if (p.mode == MODE_INT32) {
+        int4* dst = reinterpret_cast<int4*>(p.out_i32 + row * p.N + col);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            dst[k] = make_int4(__float_as_int(ab[4 * k]), __float_as_int(ab[4 * k + 1]), __float_as_int(ab[4 * k + 2]), __float_as_int(ab[4 * k + 3]));
+    } else if (p.mode == MODE_F32) {
+        float4* dst = reinterpret_cast<float4*>(p.out32 + (split * p.M + row) * p.N + col);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dst[k] = make_float4(ab[4 * k], ab[4 * k + 1], ab[4 * k + 2], ab[4 * k + 3]);
+    } else if (p.mode == MODE_F16) {
+        int4* dst = reinterpret_cast<int4*>(p.out16 + row * p.N + col);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __half2 h[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) h[u] = __floats2half2_rn(ab[8 * k + 2 * u], ab[8 * k + 2 * u + 1]);
+            dst[k] = *reinterpret_cast<int4*>(h);
         }
     } else {
-        // ------------------------------------------------------------------ consumers (8 warps)
-        const int quad = warp & 3, half_n = warp >> 2;
-        uint32_t ai = 0;
-        bool ok = true;
-        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const int64_t tile = item % num_tiles, split = item / num_tiles;
-            const int64_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const int64_t kb0 = split * p.kb_per_split;
-            const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
-            const int64_t rowblk = tm * (BM / QB) + quad;
-            const int64_t colblk0 = tn * (BN / QB) + half_n * 2;
-            const bool row_ok = rowblk < p.M / QB;
-            const bool col_ok0 = colblk0 < p.N / QB, col_ok1 = colblk0 + 1 < p.N / QB;
-
-            uint64_t acc_lo[16], acc_hi[16];   // fp32 accumulators as packed pairs: columns 0-31 and 32-63 of this thread's row
+        float m = 0.f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { acc_lo[j] = 0ull; acc_hi[j] = 0ull; }
-
-            // lane-distributed scale fetch: lanes 0-7 hold sa for 8 consecutive K blocks, 8-15 sb of column block 0, 16-23 of block 1
-            auto fetch_scales = [&](int64_t p0) -> float {
-                const int which = lane >> 3;
-                const int64_t pp = p0 + (lane & 7);
-                float v = 0.f;
-                if (pp < kb1) {
-                    if (which == 0) { if (row_ok) v = __half2float(__ldg(p.sa + rowblk * p.sa_sm + pp * p.sa_sk)); }
-                    else if (which == 1) { if (col_ok0) v = __half2float(__ldg(p.sb + colblk0 * p.sb_sn + pp * p.sb_sk)); }
-                    else if (which == 2) { if (col_ok1) v = __half2float(__ldg(p.sb + (colblk0 + 1) * p.sb_sn + pp * p.sb_sk)); }
-                }
-                return v;
-            };
-            float sc_next = INT32ACC ? 0.f : fetch_scales(kb0);
-            float sc_cur = 0.f;
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + half_n * 64;
-
-            if (INT32ACC) {
-                const uint32_t a = ai % NUM_ACC, aph = (ai / NUM_ACC) & 1u;
-                ++ai;
-                if (!(ok = bounded_wait(&acc_full[a], aph, abort_flag, 4))) break;
-                ptx::tc_fence_after();
-                uint32_t r0[32], r1[32];
-                ptx::tmem_ld_32x32b_x32(lane_base + a * BN, r0);
-                ptx::tmem_ld_32x32b_x32(lane_base + a * BN + 32, r1);
-                ptx::tmem_wait_ld_regs(r0);
-                ptx::tmem_wait_ld_regs(r1);
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
+        for (int j = 0; j < 32; ++j) m = fmaxf(m, fabsf(ab[j]));
+        const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
+        const __half sc16 = __float2half_rn(__fdiv_rn(amax, 127.0f));
+        const Divisor d = make_divisor(amax);
+        const bool zero = (amax == 0.f);
+        uint32_t words[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    acc_lo[j] = pack2(__int_as_float((int)r0[2 * j]), __int_as_float((int)r0[2 * j + 1]));
-                    acc_hi[j] = pack2(__int_as_float((int)r1[2 * j]), __int_as_float((int)r1[2 * j + 1]));
-                }
-            } else {
-                // Software pipeline over the two 32-column halves: while one half is being converted and accumulated, the
-                // tcgen05.ld of the other half (or of the next K block's first half) is in flight.
-                uint32_t r0[32], r1[32];
-                uint32_t a = ai % NUM_ACC;
-                if (!(ok = bounded_wait(&acc_full[a], (ai / NUM_ACC) & 1u, abort_flag, 4))) break;
-                ptx::tc_fence_after();
-                ptx::tmem_ld_32x32b_x32(lane_base + a * BN, r0);
-                for (int64_t kb = kb0; kb < kb1; ++kb) {
-                    const int pi = (int)((kb - kb0) & 7);
-                    if (pi == 0) {
-                        sc_cur = sc_next;
-                        sc_next = fetch_scales(kb + 8);
-                    }
-                    const float sa_v = __shfl_sync(0xffffffffu, sc_cur, pi);
-                    const float s0 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 8 + pi));
-                    const float s1 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 16 + pi));
-                    ptx::tmem_wait_ld_regs(r0);
-                    ptx::tmem_ld_32x32b_x32(lane_base + a * BN + 32, r1);
-                    scale_accumulate<CONV>(acc_lo, r0, s0);
-                    ptx::tmem_wait_ld_regs(r1);
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
-                    ++ai;
-                    if (kb + 1 < kb1) {
-                        a = ai % NUM_ACC;
-                        if (!(ok = bounded_wait(&acc_full[a], (ai / NUM_ACC) & 1u, abort_flag, 4))) break;
-                        ptx::tc_fence_after();
-                        ptx::tmem_ld_32x32b_x32(lane_base + a * BN, r0);
-                    }
-                    scale_accumulate<CONV>(acc_hi, r1, s1);
-                }
-                if (!ok) break;
-            }
-            float acc[64];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                unpack2(acc_lo[j], acc[2 * j], acc[2 * j + 1]);
-                unpack2(acc_hi[j], acc[32 + 2 * j], acc[32 + 2 * j + 1]);
-            }
-
-            // ---------------------------------------------------------------- tile epilogue
-            const int64_t row = tm * BM + quad * 32 + lane;
-            if (!row_ok) continue;
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const bool col_ok = b == 0 ? col_ok0 : col_ok1;
-                if (!col_ok) continue;   // warp-uniform
-                const int64_t col = (colblk0 + b) * QB;
-                const float* ab = &acc[32 * b];
-                if (p.mode == MODE_INT32) {
-                    int4* dst = reinterpret_cast<int4*>(p.out_i32 + row * p.N + col);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        dst[k] = make_int4(__float_as_int(ab[4 * k]), __float_as_int(ab[4 * k + 1]), __float_as_int(ab[4 * k + 2]),
-                                           __float_as_int(ab[4 * k + 3]));
-                } else if (p.mode == MODE_F32) {
-                    float4* dst = reinterpret_cast<float4*>(p.out32 + (split * p.M + row) * p.N + col);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) dst[k] = make_float4(ab[4 * k], ab[4 * k + 1], ab[4 * k + 2], ab[4 * k + 3]);
-                } else if (p.mode == MODE_F16) {
-                    int4* dst = reinterpret_cast<int4*>(p.out16 + row * p.N + col);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        __half2 h[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) h[u] = __floats2half2_rn(ab[8 * k + 2 * u], ab[8 * k + 2 * u + 1]);
-                        dst[k] = *reinterpret_cast<int4*>(h);
-                    }
+        for (int k = 0; k < 8; ++k) {
+            float nz[4] = {0.f, 0.f, 0.f, 0.f};
+            if (p.stochastic) {
+                if (p.noise) {
+                    const float4 n4 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 4 * k));
+                    nz[0] = n4.x; nz[1] = n4.y; nz[2] = n4.z; nz[3] = n4.w;
                 } else {
-                    float m = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) m = fmaxf(m, fabsf(ab[j]));
-                    const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
-                    const __half sc16 = __float2half_rn(__fdiv_rn(amax, 127.0f));
-                    const Divisor d = make_divisor(amax);
-                    const bool zero = (amax == 0.f);
-                    uint32_t words[8];
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        float nz[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (p.stochastic) {
-                            if (p.noise) {
-                                const float4 n4 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 4 * k));
-                                nz[0] = n4.x; nz[1] = n4.y; nz[2] = n4.z; nz[3] = n4.w;
-                            } else {
-                                philox_noise4((uint64_t)(row * p.N + col + 4 * k), p.seed, p.offset, nz);
-                            }
-                        }
-                        uint32_t bts[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            float v = div_exact(__fmul_rn(127.0f, ab[4 * k + u]), d);
-                            if (p.stochastic) v = __fadd_rn(v, nz[u]);
-                            v = fminf(fmaxf(v, -127.f), 127.f);
-                            bts[u] = rne_byte(v);
-                        }
-                        words[k] = zero ? 0u : pack4(bts[0], bts[1], bts[2], bts[3]);
-                    }
-                    if (p.mode == MODE_INT8) {
-                        int4* dst = reinterpret_cast<int4*>(p.out8 + row * p.N + col);
-                        dst[0] = make_int4(words[0], words[1], words[2], words[3]);
-                        dst[1] = make_int4(words[4], words[5], words[6], words[7]);
-                        if (lane == 0) p.out_scale[rowblk * (p.N / QB) + colblk0 + b] = sc16;
-                    } else {   // MODE_DEQ16
-                        const float scf = __half2float(sc16);
-                        int4* dst = reinterpret_cast<int4*>(p.out16 + row * p.N + col);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            __half h[8];
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) h[u] = deq16(sbyte(words[2 * k + (u >> 2)], u & 3), scf);
-                            dst[k] = *reinterpret_cast<int4*>(h);
-                        }
-                    }
+                    philox_noise4((uint64_t)(row * p.N + col + 4 * k), p.seed, p.offset, nz);
                 }
+            }
+            uint32_t bts[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float v = div_exact(__fmul_rn(127.0f, ab[4 * k + u]), d);
+                if (p.stochastic) v = __fadd_rn(v, nz[u]);
+                v = fminf(fmaxf(v, -127.f), 127.f);
+                bts[u] = rne_byte(v);
+            }
+            words[k] = zero ? 0u : pack4(bts[0], bts[1], bts[2], bts[3]);
+        }
+        if (p.mode == MODE_INT8) {
+            int4* dst = reinterpret_cast<int4*>(p.out8 + row * p.N + col);
+            dst[0] = make_int4(words[0], words[1], words[2], words[3]);
+            dst[1] = make_int4(words[4], words[5], words[6], words[7]);
+            if (lane == 0) p.out_scale[rowblk * (p.N / QB) + colblk] = sc16;
+        } else {   // MODE_DEQ16
+            const float scf = __half2float(sc16);
+            int4* dst = reinterpret_cast<int4*>(p.out16 + row * p.N + col);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                __half h[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) h[u] = deq16(sbyte(words[2 * k + (u >> 2)], u & 3), scf);
+                dst[k] = *reinterpret_cast<int4*>(h);
             }
         }
     }
-
-    // ---------------------------------------------------------------------- teardown
-    ptx::tc_fence_before();
-    __syncthreads();
-    if (warp == WARP_MMA) {
-        ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
-    }
 }
+
+#include "gemm_kernel.cuh"
 
 // out[i] = ((p0[i] + p1[i]) + p2[i]) + ...   then converted to the output type
 template <typename OutT>
@@ -475,7 +271,7 @@ static int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t o
 struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
-    bool attr_set[8] = {false, false, false, false, false, false, false, false};
+    bool attr_set[32] = {};
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
@@ -493,31 +289,7 @@ static int device_info(DeviceInfo** out) {
     return d.cc_major == 10 ? JF_OK : JF_ERR_UNSUPPORTED;
 }
 
-template <bool A_MN, bool B_MN, bool I32, int CONV = CONV_DEFAULT>
-static int launch_gemm(int variant, const int8_t* a, const int8_t* b, GemmParams& p, cudaStream_t st) {
-    DeviceInfo* di = nullptr;
-    if (int e = device_info(&di)) return e;
-    auto kern = gemm_kernel<A_MN, B_MN, I32, CONV>;
-    {
-        std::lock_guard<std::mutex> lock(g_dev_mutex);
-        if (!di->attr_set[variant]) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM) != cudaSuccess)
-                return JF_ERR_LAUNCH;
-            di->attr_set[variant] = true;
-        }
-    }
-    CUtensorMap ma, mb;
-    // K-major operand: [rows, K] row-major -> inner = K.  MN-major operand: [K, rows] row-major -> inner = rows.
-    if (int e = A_MN ? make_map(&ma, a, p.M, p.K, p.M) : make_map(&ma, a, p.K, p.M, p.K)) return e;
-    if (int e = B_MN ? make_map(&mb, b, p.N, p.K, p.N) : make_map(&mb, b, p.K, p.N, p.K)) return e;
-    p.tiles_m = (p.M + BM - 1) / BM;
-    p.tiles_n = (p.N + BN - 1) / BN;
-    p.nkb = p.K / QB;
-    const int64_t items = p.tiles_m * p.tiles_n * p.splits;
-    const unsigned grid = (unsigned)(items < di->sm_count ? items : di->sm_count);
-    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, p);
-    return check_launch();
-}
+#include "gemm_launch.inc"
 
 static int plan_splits(int64_t M, int64_t N, int64_t K, int split_k, int sm_count, int64_t* per_out) {
     const int64_t nkb = K / QB;
@@ -568,14 +340,7 @@ int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t s
     } else {
         return JF_ERR_ARG;
     }
-    cudaStream_t st = (cudaStream_t)stream;
-    static const int conv = [] { const char* e = getenv("JF_GEMM_CONV"); return e ? atoi(e) : (int)CONV_DEFAULT; }();
-    switch (conv) {   // tuning switch for the conversion strategy of the forward kernel
-        case CONV_I2F: return launch_gemm<false, false, false, CONV_I2F>(4, x, w, p, st);
-        case CONV_MAGIC_SCALAR: return launch_gemm<false, false, false, CONV_MAGIC_SCALAR>(5, x, w, p, st);
-        case CONV_MIXED: return launch_gemm<false, false, false, CONV_MIXED>(6, x, w, p, st);
-        default: return launch_gemm<false, false, false, CONV_MAGIC>(0, x, w, p, st);
-    }
+    return launch_fwd(x, w, p, (cudaStream_t)stream);
 }
 
 int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_stride_m, int64_t sg_stride_k, const void* sw,
@@ -600,7 +365,7 @@ int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_
     } else {
         return JF_ERR_ARG;
     }
-    return launch_gemm<false, true, false>(1, g, w, p, (cudaStream_t)stream);
+    return launch_dgrad_layout(g, w, p, (cudaStream_t)stream);
 }
 
 int jf_igemm_wgrad_plan(int64_t M, int64_t N, int64_t K, int split_k) {
@@ -630,12 +395,12 @@ int jf_igemm_wgrad(const int8_t* g, int g_transposed, const int8_t* x, const voi
     if (splits == 1) {
         if (out_dtype == JF_F16) { p.mode = MODE_F16; p.out16 = (__half*)dw; }
         else { p.mode = MODE_F32; p.out32 = (float*)dw; }
-        return g_transposed ? launch_gemm<false, true, false>(1, g, x, p, st) : launch_gemm<true, true, false>(2, g, x, p, st);
+        return g_transposed ? launch_dgrad_layout(g, x, p, st) : launch_wgrad_layout(g, x, p, st);
     }
     if (!scratch) return JF_ERR_NULL;
     if (!aligned16(scratch)) return JF_ERR_ALIGN;
     p.mode = MODE_F32; p.out32 = scratch;
-    if (int e = g_transposed ? launch_gemm<false, true, false>(1, g, x, p, st) : launch_gemm<true, true, false>(2, g, x, p, st)) return e;
+    if (int e = g_transposed ? launch_dgrad_layout(g, x, p, st) : launch_wgrad_layout(g, x, p, st)) return e;
     const int64_t count = M * N;
     const unsigned grid = (unsigned)((count / 4 + 255) / 256);
     if (out_dtype == JF_F16) splitk_reduce_kernel<__half><<<grid, 256, 0, st>>>(scratch, splits, count, (__half*)dw);
@@ -650,7 +415,7 @@ int jf_igemm_int32(const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64
     GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.splits = 1; p.kb_per_split = K / QB;
     p.mode = MODE_INT32; p.out_i32 = c;
-    return launch_gemm<false, false, true>(3, a, b, p, (cudaStream_t)stream);
+    return launch_int32(a, b, p, (cudaStream_t)stream);
 }
 
 /* Reads (and clears) the device-side error flag raised when a bounded wait inside the GEMM kernel expired.
