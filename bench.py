@@ -169,6 +169,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     from jetfire_int8training_b200 import Linear, Nonlinear, rng
+    from jetfire_int8training_b200.dp import allreduce_mean_
     from jetfire_int8training_b200._lib import lib
     L = lib()
     rng.manual_seed(1234 + rank)
@@ -195,7 +196,7 @@ def run_ours(args):
             e1.record(); fwd_ev.append((e0, e1))
         gx8, gsx, gw = Linear.int8_linear_backward(X8, SX, G8, SG, None, W8, SW, 32, stochastic=True)
         if world > 1:
-            dist.all_reduce(gw)
+            allreduce_mean_([gw])
         return y8, sy, gx8, gsx, gw
 
     for _ in range(args.warmup):
@@ -251,7 +252,7 @@ def run_ours(args):
         y8, sy = Linear.int8_linear_forward(x8, sx, w8, sw, True, 32)
         gx8, gsx, gw = Linear.int8_linear_backward(x8, sx, g8, sg, None, w8, sw, 32, stochastic=True)
         if world > 1:
-            dist.all_reduce(gw)
+            allreduce_mean_([gw])
         for h, o in zip(host_out, (y8, sy, gx8, gsx, gw)):
             h.copy_(o, non_blocking=True)
     e2e_steps = max(2, min(args.steps, 5))

@@ -12,9 +12,10 @@
  *   - M and N (and K) must be positive multiples of 32; payload pointers must be 16-byte aligned;
  *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream),
  *     allocates nothing, never synchronises, and returns 0 on success or a negative jf_status;
- *   - stochastic rounding uses a counter-based Philox4x32-10 keyed by (seed, offset): element e = row*N+col
- *     takes word e%4 of the block with counter (e/4, offset); passing a non-NULL `noise` (fp32 [M,N], values in
- *     [-0.5,0.5)) overrides the generator (used to reproduce the reference bit for bit in tests).
+ *   - stochastic rounding uses a counter-based Philox4x32-10 keyed by (seed, offset): one call with counter (e/8, offset)
+ *     serves the 8 elements e = row*N+col .. +7; element e takes the 16-bit half (e & 1) of word (e >> 1) & 3 and
+ *     noise = h * 2^-16 - 0.5.  Passing a non-NULL `noise` (fp32 [M,N], values in [-0.5,0.5)) overrides the generator
+ *     (used to reproduce the reference bit for bit in tests).
  */
 #ifndef JETFIRE_B200_H
 #define JETFIRE_B200_H

@@ -171,25 +171,29 @@ __device__ __forceinline__ void store_block(const GemmParams& p, const float (&a
         const bool zero = (amax == 0.f);
         uint32_t words[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            float nz[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k8 = 0; k8 < 4; ++k8) {      // 8 elements = one Philox call
+            float nz[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (p.stochastic) {
                 if (p.noise) {
-                    const float4 n4 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 4 * k));
-                    nz[0] = n4.x; nz[1] = n4.y; nz[2] = n4.z; nz[3] = n4.w;
+                    const float4 n0 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8));
+                    const float4 n1 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8 + 4));
+                    nz[0] = n0.x; nz[1] = n0.y; nz[2] = n0.z; nz[3] = n0.w; nz[4] = n1.x; nz[5] = n1.y; nz[6] = n1.z; nz[7] = n1.w;
                 } else {
-                    philox_noise4((uint64_t)(row * p.N + col + 4 * k), p.seed, p.offset, nz);
+                    philox_noise8((uint64_t)(row * p.N + col + 8 * k8), p.seed, p.offset, nz);
                 }
             }
-            uint32_t bts[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                float v = div_exact(__fmul_rn(127.0f, ab[4 * k + u]), d);
-                if (p.stochastic) v = __fadd_rn(v, nz[u]);
-                v = fminf(fmaxf(v, -127.f), 127.f);
-                bts[u] = rne_byte(v);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t bts[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    float v = div_exact(__fmul_rn(127.0f, ab[8 * k8 + 4 * h + u]), d);
+                    if (p.stochastic) v = __fadd_rn(v, nz[4 * h + u]);
+                    v = fminf(fmaxf(v, -127.f), 127.f);
+                    bts[u] = rne_byte(v);
+                }
+                words[2 * k8 + h] = zero ? 0u : pack4(bts[0], bts[1], bts[2], bts[3]);
             }
-            words[k] = zero ? 0u : pack4(bts[0], bts[1], bts[2], bts[3]);
         }
         if (p.mode == MODE_INT8) {
             int4* dst = reinterpret_cast<int4*>(p.out8 + row * p.N + col);

@@ -44,21 +44,24 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
     return c;
 }
 
-// word -> noise in (-0.5, 0.5): ((w >> 9) - 2^22 + 0.5) * 2^-23, exact in fp32.
-__device__ __forceinline__ float word_to_noise(uint32_t w) {
-    const int k = (int)(w >> 9) - (1 << 22);
-    return __fadd_rn(__fmul_rn((float)k, 1.1920928955078125e-07f), 5.9604644775390625e-08f);
+// Noise mapping.  One Philox call (four 32-bit words) serves the 8 consecutive elements of group g = e / 8; element e uses the
+// 16-bit half (e & 1) of word (e >> 1) & 3:  noise = h * 2^-16 - 0.5, a multiple of 2^-16 in [-0.5, 0.5) like the reference's
+// uniform_(-0.5, 0.5).  Built without an int->float conversion: the half is placed in the low mantissa bits of 2^23, and one
+// FMA rescales it: (2^23 + h) * 2^-16 - 128.5 = h * 2^-16 - 0.5, exact in fp32.
+__device__ __forceinline__ float half_to_noise(uint32_t w, int hi) {
+    const uint32_t bits = __byte_perm(w, 0x4B000000u, hi ? 0x7432 : 0x7410);   // {h.lo, h.hi, 0x00, 0x4B}
+    return __fmaf_rn(__uint_as_float(bits), 1.52587890625e-05f, -128.5f);
 }
 
-// Noise for the 4 consecutive elements starting at linear index e (e % 4 == 0).
-__device__ __forceinline__ void philox_noise4(uint64_t e, uint64_t seed, uint64_t offset, float out[4]) {
-    const uint64_t g = e >> 2;
+// Noise for the 8 consecutive elements starting at linear index e (e % 8 == 0).
+__device__ __forceinline__ void philox_noise8(uint64_t e, uint64_t seed, uint64_t offset, float out[8]) {
+    const uint64_t g = e >> 3;
     const uint4 w = philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), (uint32_t)offset, (uint32_t)(offset >> 32)),
                                   make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
-    out[0] = word_to_noise(w.x);
-    out[1] = word_to_noise(w.y);
-    out[2] = word_to_noise(w.z);
-    out[3] = word_to_noise(w.w);
+    out[0] = half_to_noise(w.x, 0); out[1] = half_to_noise(w.x, 1);
+    out[2] = half_to_noise(w.y, 0); out[3] = half_to_noise(w.y, 1);
+    out[4] = half_to_noise(w.z, 0); out[5] = half_to_noise(w.z, 1);
+    out[6] = half_to_noise(w.w, 0); out[7] = half_to_noise(w.w, 1);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -111,6 +114,26 @@ __device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2,
 __device__ __forceinline__ __half deq16(int q, float s_as_float) { return __float2half_rn(__fmul_rn((float)q, s_as_float)); }
 
 __device__ __forceinline__ int sbyte(uint32_t w, int i) { return (int)(int8_t)(w >> (8 * i)); }
+
+// Exact int8 -> fp32 without the conversion unit: byte k of w (two's complement), with its sign bit flipped, goes into the low
+// mantissa byte of 2^23; (2^23 + u) - (2^23 + 128) = q exactly.  `wx` must be w ^ 0x80808080.
+__device__ __forceinline__ float byte_to_float(uint32_t wx, int k) {
+    const uint32_t sel = k == 0 ? 0x7440u : k == 1 ? 0x7441u : k == 2 ? 0x7442u : 0x7443u;   // {byte k, 0x00, 0x00, 0x4B}
+    return __fadd_rn(__uint_as_float(__byte_perm(wx, 0x4B000000u, sel)), -8388736.0f);
+}
+
+// 1 - erf(|z|) * ... building block of the GELU kernels: for u = |x| / sqrt(2),
+//   erfc(u) ~= t * (a1 + t*(a2 + t*(a3 + t*(a4 + t*a5)))) * exp(-u^2),  t = 1 / (1 + p*u)        (Abramowitz-Stegun 7.1.26,
+// absolute error <= 1.5e-7).  Returns the polynomial factor; the caller multiplies by exp(-x^2/2), which the backward kernel
+// needs anyway for the density term.
+__device__ __forceinline__ float erfc_poly(float u) {
+    const float t = __frcp_rn(__fmaf_rn(0.3275911f, u, 1.0f));
+    float q = __fmaf_rn(1.061405429f, t, -1.453152027f);
+    q = __fmaf_rn(q, t, 1.421413741f);
+    q = __fmaf_rn(q, t, -0.284496736f);
+    q = __fmaf_rn(q, t, 0.254829592f);
+    return __fmul_rn(q, t);
+}
 
 // dtype-generic 16-element row chunk loads -> fp32
 template <typename T>

@@ -1,14 +1,21 @@
 // INT8-in / INT8-out nonlinear operators of the Jetfire data flow, written for sm_100a.
 //
-// All kernels are bandwidth-bound streaming kernels built on one work decomposition:
-//   * a warp owns a tile of 32 rows x 128 columns = four 32x32 quantisation blocks;
-//   * lane = (rg, cc) with rg = lane / 8 (row group) and cc = lane % 8 (16-column chunk); in pass i (0..7) the lane
-//     touches row 4*i + rg, columns [16*cc, 16*cc + 16): one 16-byte access per int8 row chunk, so a warp-wide
-//     access covers four full 128-byte lines and every thread keeps 8 independent 16-byte loads in flight;
-//   * a quantisation block is held by the 8 lanes {cc in {2b, 2b+1}} x {rg 0..3}; its absmax is three
-//     __shfl_xor steps (lane masks 1, 8, 16);
-//   * the re-quantising division is an exact IEEE quotient computed with a shared correctly-rounded reciprocal.
-// CTAs are 8 warps; consecutive warps take consecutive tiles (row-major over the tile grid).
+// All kernels are streaming kernels built on one work decomposition:
+//   * a warp owns a tile of 32 rows x TW columns (TW = 64 or 128, i.e. two or four 32x32 quantisation blocks);
+//   * a lane owns a 16-column chunk: with LPR = TW/16 lanes per row, lane = (rg, cc), rg = lane / LPR (row group),
+//     cc = lane % LPR (chunk); in pass i (0 .. LPR-1) the lane touches row i*(32/LPR) + rg, columns [16*cc, 16*cc + 16):
+//     one 16-byte access per int8 row chunk, every access of a warp covers whole 64/128-byte row segments, and all loads of a
+//     tile are issued before the first use;
+//   * a quantisation block is held by lanes {cc in {2b, 2b+1}} x all rg; its absmax is a thread-local max plus __shfl_xor
+//     steps over lane bit 0 and the rg bits;
+//   * the re-quantising division is an exact IEEE quotient computed with a shared correctly-rounded reciprocal (fast path
+//     chosen once per warp), rounding is an add of 1.5*2^23, bytes are gathered with prmt;
+//   * int8 -> fp32 avoids the conversion unit (prmt into the mantissa of 2^23, one subtract).
+// The narrow tile (64 values per thread) keeps the register count low enough for 3 CTAs of 8 warps per SM, which is what keeps
+// enough loads in flight to approach HBM bandwidth; kernels that need a 128-column slab (LayerNorm backward, residual add with
+// row statistics) use the wide tile.
+#include <cstdlib>
+
 #include "jf_common.cuh"
 
 namespace jf {
@@ -17,7 +24,13 @@ thread_local int g_last_cuda_error = 0;
 
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int TILE_N = 128;
+
+template <int TW>
+struct Geo {
+    static constexpr int LPR = TW / 16;      // lanes per tile row
+    static constexpr int RPP = 32 / LPR;     // rows per pass
+    static constexpr int NP = LPR;           // passes (NP * RPP = 32 rows)
+};
 
 struct Tile {
     int64_t tm, tn;   // tile coordinates
@@ -27,39 +40,94 @@ struct Tile {
     bool active;      // the chunk lies inside the tensor (N may end inside the tile)
 };
 
-__device__ __forceinline__ bool tile_setup(int64_t M, int64_t N, Tile& t) {
-    const int warp = threadIdx.x >> 5;
+template <int TW>
+__device__ __forceinline__ Tile make_tile(int64_t tile, int64_t tiles_n, int64_t N) {
+    Tile t;
     t.lane = threadIdx.x & 31;
-    const int64_t tiles_n = (N + TILE_N - 1) / TILE_N;
-    const int64_t tile = (int64_t)blockIdx.x * WARPS + warp;
-    if (tile >= (M / QB) * tiles_n) return false;
     t.tm = tile / tiles_n;
     t.tn = tile % tiles_n;
-    t.rg = t.lane >> 3;
-    t.cc = t.lane & 7;
+    t.rg = t.lane / Geo<TW>::LPR;
+    t.cc = t.lane % Geo<TW>::LPR;
     t.row0 = t.tm * QB;
-    t.col = t.tn * TILE_N + t.cc * 16;
+    t.col = t.tn * TW + t.cc * 16;
     t.active = t.col < N;
-    return true;
+    return t;
 }
 
-static inline unsigned grid_for(int64_t M, int64_t N) {
-    const int64_t tiles = (M / QB) * ((N + TILE_N - 1) / TILE_N);
-    return (unsigned)((tiles + WARPS - 1) / WARPS);
+// Persistent loop of one warp over its tiles (tile index = blockIdx.x*WARPS + warp, stride gridDim.x*WARPS).  The loads of the
+// NEXT tile are issued before the current tile is processed, so every warp keeps memory requests in flight while it computes.
+//   load(const Tile&, Raw&)  : issue the global loads of a tile into registers
+//   proc(const Tile&, Raw&)  : compute and store the tile
+template <int TW, class Raw, bool PREFETCH, class LoadF, class ProcF>
+__device__ __forceinline__ void for_each_tile(int64_t M, int64_t N, LoadF&& load, ProcF&& proc) {
+    const int64_t tiles_n = (N + TW - 1) / TW, total = (M / QB) * tiles_n;
+    const int64_t stride = (int64_t)gridDim.x * WARPS;
+    int64_t tile = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (tile >= total) return;
+    Tile t = make_tile<TW>(tile, tiles_n, N);
+    Raw cur;
+    load(t, cur);
+    for (;;) {
+        const int64_t next = tile + stride;
+        const bool has_next = next < total;
+        Tile tn = t;
+        Raw nxt;
+        if (has_next) {
+            tn = make_tile<TW>(next, tiles_n, N);
+            if (PREFETCH) load(tn, nxt);
+        }
+        proc(t, cur);
+        if (!has_next) break;
+        if (PREFETCH) cur = nxt;
+        else load(tn, cur);
+        t = tn;
+        tile = next;
+    }
 }
 
+template <int TW>
+__device__ __forceinline__ int64_t row_of(const Tile& t, int i) { return t.row0 + i * Geo<TW>::RPP + t.rg; }
+
+// number of CTAs: all tiles if they fit in `max_ctas`, else a persistent grid
+template <int TW>
+static inline unsigned grid_for(int64_t M, int64_t N, int max_ctas = 0) {
+    const int64_t tiles = (M / QB) * ((N + TW - 1) / TW);
+    const int64_t ctas = (tiles + WARPS - 1) / WARPS;
+    return (unsigned)((max_ctas > 0 && ctas > max_ctas) ? max_ctas : ctas);
+}
+
+// max over the 32x32 block this lane belongs to (lane bit 0 = the two chunks of the block, then every rg bit)
+template <int TW>
 __device__ __forceinline__ float block_max(float m) {
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+#pragma unroll
+    for (int mask = Geo<TW>::LPR; mask < 32; mask <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, mask));
     return m;
+}
+// sum over the lanes of one tile row (the cc bits)
+template <int TW>
+__device__ __forceinline__ float row_sum(float a) {
+#pragma unroll
+    for (int mask = 1; mask < Geo<TW>::LPR; mask <<= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, mask));
+    return a;
+}
+// sum over the row groups (the rg bits): afterwards every lane holds the column sum over the tile's 32 rows
+template <int TW>
+__device__ __forceinline__ float col_sum(float a) {
+#pragma unroll
+    for (int mask = Geo<TW>::LPR; mask < 32; mask <<= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, mask));
+    return a;
 }
 
 struct SrCfg {
-    int stochastic;
     const float* noise;
     uint64_t seed, offset;
 };
+
+// low bytes of four registers -> one word
+__device__ __forceinline__ uint32_t gather_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
 
 // 4x4 byte transpose: in w[k] = row k (4 column bytes); out o[j] = column j (4 row bytes).
 __device__ __forceinline__ void transpose4x4(const uint32_t w[4], uint32_t o[4]) {
@@ -71,45 +139,55 @@ __device__ __forceinline__ void transpose4x4(const uint32_t w[4], uint32_t o[4])
     o[3] = __byte_perm(t2, t3, 0x7632);
 }
 
-// Write the warp's 32x128 int8 tile, staged in shared memory (row-major, 128 B per row), transposed to qt[N, M].
-// Lane l owns tile columns 4l..4l+3 and emits, per column, two 16-byte stores (rows 0-15 and 16-31).
-__device__ __forceinline__ void store_tile_transposed(const uint32_t* tile_words, const Tile& t, int64_t M, int64_t N,
-                                                      int8_t* qt) {
-    uint32_t colw[4][8];
+// Write the warp's 32 x TW int8 tile, staged in shared memory (row-major, TW bytes per row), transposed to qt[N, M].
+// TW/4 column groups of 4 columns; lane l owns column group l % (TW/4) and the row range 32/(128/TW) * (l / (TW/4)):
+//   TW = 128: 32 groups x 32 rows (two 16-byte stores per column); TW = 64: 16 groups x 16 rows (one 16-byte store per column).
+template <int TW>
+__device__ __forceinline__ void store_tile_transposed(const uint32_t* tile_words, const Tile& t, int64_t M, int64_t N, int8_t* qt) {
+    constexpr int WPR = TW / 4;             // words per tile row = column groups
+    constexpr int ROWS = 32 * WPR / 32;     // rows handled per lane (32 or 16)
+    const int cg = t.lane % WPR, r0 = (t.lane / WPR) * ROWS;
+    uint32_t colw[4][ROWS / 4];
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
+    for (int g = 0; g < ROWS / 4; ++g) {
         uint32_t w[4], o[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) w[k] = tile_words[(4 * g + k) * 32 + t.lane];
+        for (int k = 0; k < 4; ++k) w[k] = tile_words[(r0 + 4 * g + k) * WPR + cg];
         transpose4x4(w, o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) colw[j][g] = o[j];
     }
-    const int64_t c0 = t.tn * TILE_N + 4 * t.lane;
+    const int64_t c0 = t.tn * TW + 4 * cg;
     if (c0 < N) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            int4* dst = reinterpret_cast<int4*>(qt + (c0 + j) * M + t.row0);
-            dst[0] = make_int4(colw[j][0], colw[j][1], colw[j][2], colw[j][3]);
-            dst[1] = make_int4(colw[j][4], colw[j][5], colw[j][6], colw[j][7]);
+            int4* dst = reinterpret_cast<int4*>(qt + (c0 + j) * M + t.row0 + r0);
+#pragma unroll
+            for (int h = 0; h < ROWS / 16; ++h) dst[h] = make_int4(colw[j][4 * h], colw[j][4 * h + 1], colw[j][4 * h + 2], colw[j][4 * h + 3]);
         }
     }
 }
 
-// Quantise the lane's 8x16 values with the block scale `scale32` (= block absmax (+adj) / 127, identical in the 8
-// lanes of a block) and store payload + scale.  TRUNC selects the truncating conversion of the residual-add kernels.
-template <bool TRUNC, bool TRANSPOSE>
-__device__ __forceinline__ void emit_quantized(const float (&v)[8][16], float scale32, const Tile& t, int64_t M, int64_t N,
+// Quantise the lane's NP x 16 values (row i delivered by rowf(i, a)) with the block scale `scale32` (= block absmax (+adj) / 127, identical in the lanes of a
+// block) and store payload + scale.  TRUNC selects the truncating conversion of the residual-add kernels; SR the stochastic
+// pre-step sign(v) * min(|v| + noise, 127) of the reference (its lower clamp at -128 can never bind).
+template <int TW, bool TRUNC, bool SR, bool TRANSPOSE, class RowF>
+__device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const Tile& t, int64_t M, int64_t N,
                                                int8_t* q, __half* s, const SrCfg& sr, uint32_t* tile_words, int8_t* qt) {
+    constexpr int NP = Geo<TW>::NP;
     const Divisor d = make_divisor(scale32);
     const bool zero = (scale32 == 0.f);
+    // one decision per warp: the Markstein path is exact only inside its exponent window
+    const bool fast = __all_sync(0xffffffffu, d.fast || zero);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int64_t row = t.row0 + 4 * i + t.rg;
-        uint32_t words[4];
+    for (int i = 0; i < NP; ++i) {
+        const int64_t row = row_of<TW>(t, i);
+        uint32_t words[4] = {0u, 0u, 0u, 0u};
         if (t.active) {
+            float av[16];
+            rowf(i, av);
             float nz[16];
-            if (sr.stochastic) {
+            if (SR) {
                 if (sr.noise) {
                     const float4* np4 = reinterpret_cast<const float4*>(sr.noise + row * N + t.col);
 #pragma unroll
@@ -118,8 +196,8 @@ __device__ __forceinline__ void emit_quantized(const float (&v)[8][16], float sc
                         nz[4 * k] = n4.x; nz[4 * k + 1] = n4.y; nz[4 * k + 2] = n4.z; nz[4 * k + 3] = n4.w;
                     }
                 } else {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) philox_noise4((uint64_t)(row * N + t.col) + 4 * k, sr.seed, sr.offset, &nz[4 * k]);
+                    philox_noise8((uint64_t)(row * N + t.col), sr.seed, sr.offset, &nz[0]);
+                    philox_noise8((uint64_t)(row * N + t.col) + 8, sr.seed, sr.offset, &nz[8]);
                 }
             }
 #pragma unroll
@@ -127,235 +205,382 @@ __device__ __forceinline__ void emit_quantized(const float (&v)[8][16], float sc
                 uint32_t b[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    float x = div_exact(v[i][4 * k + j], d);
-                    if (sr.stochastic) x = sr_prestep(x, nz[4 * k + j]);
-                    b[j] = TRUNC ? trunc_byte(x) : rne_byte(x);
+                    const float a = av[4 * k + j];
+                    float x;
+                    if (fast) {
+                        const float q0 = __fmul_rn(a, d.inv);
+                        x = __fmaf_rn(__fmaf_rn(-d.b, q0, a), d.inv, q0);
+                    } else {
+                        x = __fdiv_rn(a, d.b);
+                    }
+                    if (SR) {
+                        const float mag = fminf(__fadd_rn(fabsf(x), nz[4 * k + j]), 127.f);
+                        x = __uint_as_float(__float_as_uint(mag) ^ (__float_as_uint(x) & 0x80000000u));
+                    }
+                    b[j] = TRUNC ? (uint32_t)__float2int_rz(x) : __float_as_uint(__fadd_rn(x, 12582912.0f));
                 }
-                words[k] = zero ? 0u : pack4(b[0], b[1], b[2], b[3]);
+                words[k] = zero ? 0u : gather_bytes(b[0], b[1], b[2], b[3]);
             }
             *reinterpret_cast<int4*>(q + row * N + t.col) = make_int4(words[0], words[1], words[2], words[3]);
-        } else {
-            words[0] = words[1] = words[2] = words[3] = 0u;
         }
         if (TRANSPOSE) {
-            uint32_t* dst = tile_words + (4 * i + t.rg) * 32 + t.cc * 4;
+            uint32_t* dst = tile_words + (i * Geo<TW>::RPP + t.rg) * (TW / 4) + t.cc * 4;
             *reinterpret_cast<int4*>(dst) = make_int4(words[0], words[1], words[2], words[3]);
         }
     }
     if (t.active && t.rg == 0 && (t.cc & 1) == 0) s[t.tm * (N / QB) + (t.col >> 5)] = __float2half_rn(scale32);
     if (TRANSPOSE) {
         __syncwarp();
-        store_tile_transposed(tile_words, t, M, N, qt);
+        store_tile_transposed<TW>(tile_words, t, M, N, qt);
+        __syncwarp();   // the tile buffer is reused by the warp's next tile
     }
 }
 
-__device__ __forceinline__ float absmax_8x16(const float (&v)[8][16]) {
+template <int NP>
+__device__ __forceinline__ float absmax_tile(const float (&v)[NP][16]) {
     float m = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < NP; ++i)
 #pragma unroll
         for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(v[i][j]));
     return m;
 }
 
-// Load the lane's 8 int8 row chunks (16 B each); inactive lanes get zeros.
-__device__ __forceinline__ void load_q(const int8_t* q, const Tile& t, int64_t N, int4 (&raw)[8]) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        raw[i] = t.active ? __ldg(reinterpret_cast<const int4*>(q + (t.row0 + 4 * i + t.rg) * N + t.col)) : make_int4(0, 0, 0, 0);
-    }
-}
 __device__ __forceinline__ float load_scale(const __half* s, const Tile& t, int64_t N) {
     return t.active ? __half2float(__ldg(s + t.tm * (N / QB) + (t.col >> 5))) : 0.f;
 }
-__device__ __forceinline__ int q_at(const int4& r, int j) {
-    const uint32_t w = (j < 4) ? (uint32_t)r.x : (j < 8) ? (uint32_t)r.y : (j < 12) ? (uint32_t)r.z : (uint32_t)r.w;
-    return sbyte(w, j & 3);
+// the 16 payload values of one row chunk as exact fp32
+__device__ __forceinline__ void unpack16(const int4& r, float (&f)[16]) {
+    const uint32_t w[4] = {(uint32_t)r.x ^ 0x80808080u, (uint32_t)r.y ^ 0x80808080u, (uint32_t)r.z ^ 0x80808080u, (uint32_t)r.w ^ 0x80808080u};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) f[4 * k + j] = byte_to_float(w[k], j);
+}
+// fp16-rounded dequantisation fp32(fp16(q) * s) of one row chunk (the reference's int8 * fp16 product), two values at a time
+__device__ __forceinline__ void dequant16_h(const int4& r, __half2 s2, float (&f)[16]) {
+    float qf[16];
+    unpack16(r, qf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float2 p = __half22float2(__hmul2_rn(__floats2half2_rn(qf[2 * j], qf[2 * j + 1]), s2));
+        f[2 * j] = p.x; f[2 * j + 1] = p.y;
+    }
+}
+
+__device__ __forceinline__ __half2 load_scale_h2(const __half* s, const Tile& t, int64_t N) {
+    return t.active ? __half2half2(__ldg(s + t.tm * (N / QB) + (t.col >> 5))) : __half2half2(__float2half_rn(0.f));
+}
+
+// Raw (still packed) register images of a tile's inputs, as the loads deliver them.
+template <int NP>
+struct RawQ {          // one int8 tensor + its block scale
+    int4 d[NP];
+    __half sc;
+};
+template <int NP>
+struct RawQ2 {         // two int8 tensors + their block scales
+    int4 a[NP], b[NP];
+    __half sa, sb;
+};
+template <typename T, int NP>
+struct RawX {          // one tensor of T: 16 elements = sizeof(T) 16-byte words per row chunk
+    uint4 d[NP][sizeof(T)];
+};
+
+template <int TW>
+__device__ __forceinline__ void load_rows(const int8_t* q, const Tile& t, int64_t N, int4 (&raw)[Geo<TW>::NP]) {
+#pragma unroll
+    for (int i = 0; i < Geo<TW>::NP; ++i)
+        raw[i] = t.active ? __ldg(reinterpret_cast<const int4*>(q + row_of<TW>(t, i) * N + t.col)) : make_int4(0, 0, 0, 0);
+}
+__device__ __forceinline__ __half load_scale16(const __half* s, const Tile& t, int64_t N) {
+    return t.active ? __ldg(s + t.tm * (N / QB) + (t.col >> 5)) : __float2half_rn(0.f);
+}
+template <typename T, int TW>
+__device__ __forceinline__ void load_x(const T* x, const Tile& t, int64_t N, RawX<T, Geo<TW>::NP>& r) {
+#pragma unroll
+    for (int i = 0; i < Geo<TW>::NP; ++i) {
+        const uint4* p4 = reinterpret_cast<const uint4*>(x + row_of<TW>(t, i) * N + t.col);
+#pragma unroll
+        for (int k = 0; k < (int)sizeof(T); ++k) r.d[i][k] = t.active ? __ldg(p4 + k) : make_uint4(0, 0, 0, 0);
+    }
+}
+// 16 values of T (held as sizeof(T) 16-byte words) -> fp32
+__device__ __forceinline__ void widen16(const uint4 (&d)[4], float (&v)[16], float) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        v[4 * k] = __uint_as_float(d[k].x); v[4 * k + 1] = __uint_as_float(d[k].y);
+        v[4 * k + 2] = __uint_as_float(d[k].z); v[4 * k + 3] = __uint_as_float(d[k].w);
+    }
+}
+__device__ __forceinline__ void widen16(const uint4 (&d)[2], float (&v)[16], __half) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t w[4] = {d[k].x, d[k].y, d[k].z, d[k].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            v[8 * k + 2 * j] = f.x; v[8 * k + 2 * j + 1] = f.y;
+        }
+    }
+}
+__device__ __forceinline__ void widen16(const uint4 (&d)[2], float (&v)[16], __nv_bfloat16) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t w[4] = {d[k].x, d[k].y, d[k].z, d[k].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[8 * k + 2 * j] = __uint_as_float(w[j] << 16);
+            v[8 * k + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+    }
 }
 
 // =========================================================================================================
-// quantize / quantize_transpose
+// quantize / quantize_transpose.  The tile stays packed in registers; it is widened once for the block absmax and once more
+// for the quantisation, which is cheaper than holding 64 fp32 values next to the prefetched next tile.
 // =========================================================================================================
-template <typename T, bool TRANSPOSE>
-__global__ void __launch_bounds__(THREADS) quantize_kernel(const T* __restrict__ x, int64_t M, int64_t N, int8_t* __restrict__ q,
-                                                           __half* __restrict__ s, int8_t* __restrict__ qt, SrCfg sr) {
-    __shared__ __align__(16) uint32_t smem_tiles[TRANSPOSE ? WARPS * 32 * 32 : 1];
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    float v[8][16];
+template <typename T, int TW, bool SR, bool TRANSPOSE>
+__global__ void __launch_bounds__(THREADS, 2)
+quantize_kernel(const T* __restrict__ x, int64_t M, int64_t N, int8_t* __restrict__ q, __half* __restrict__ s,
+                int8_t* __restrict__ qt, SrCfg sr) {
+    constexpr int NP = Geo<TW>::NP;
+    using Raw = RawX<T, NP>;
+    __shared__ __align__(16) uint32_t smem_tiles[TRANSPOSE ? WARPS * 8 * TW : 1];
+    uint32_t* tile_words = TRANSPOSE ? smem_tiles + (threadIdx.x >> 5) * 8 * TW : nullptr;
+    // fp32 input: the packed tile is already 64 registers, prefetching a second one would spill
+    for_each_tile<TW, Raw, sizeof(T) != 4>(
+        M, N, [&](const Tile& t, Raw& r) { load_x<T, TW>(x, t, N, r); },
+        [&](const Tile& t, Raw& r) {
+            float m = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (t.active) {
-            Load16<T>::load(x + (t.row0 + 4 * i + t.rg) * N + t.col, v[i]);
-        } else {
+            for (int i = 0; i < NP; ++i) {
+                float a[16];
+                widen16(r.d[i], a, T());
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
-        }
-    }
-    const float amax = block_max(absmax_8x16(v));
-    const float scale32 = __fdiv_rn(amax, 127.0f);
-    emit_quantized<false, TRANSPOSE>(v, scale32, t, M, N, q, s, sr, TRANSPOSE ? smem_tiles + (threadIdx.x >> 5) * 1024 : nullptr, qt);
+                for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(a[j]));
+            }
+            const float scale32 = __fdiv_rn(block_max<TW>(m), 127.0f);
+            emit_quantized<TW, false, SR, TRANSPOSE>([&](int i, float (&a)[16]) { widen16(r.d[i], a, T()); }, scale32, t, M, N, q, s, sr,
+                                                     tile_words, qt);
+        });
 }
 
 // =========================================================================================================
 // dequantize: y = fp32(fp16(q) * s)
 // =========================================================================================================
-__global__ void __launch_bounds__(THREADS) dequantize_kernel(const int8_t* __restrict__ q, const __half* __restrict__ s, int64_t M,
-                                                             int64_t N, float* __restrict__ y) {
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    if (!t.active) return;
-    int4 raw[8];
-    load_q(q, t, N, raw);
-    const float sc = load_scale(s, t, N);
+template <int TW>
+__global__ void __launch_bounds__(THREADS, 2)
+dequantize_kernel(const int8_t* __restrict__ q, const __half* __restrict__ s, int64_t M, int64_t N, float* __restrict__ y) {
+    constexpr int NP = Geo<TW>::NP;
+    using Raw = RawQ<NP>;
+    for_each_tile<TW, Raw, true>(
+        M, N,
+        [&](const Tile& t, Raw& r) {
+            load_rows<TW>(q, t, N, r.d);
+            r.sc = load_scale16(s, t, N);
+        },
+        [&](const Tile& t, Raw& r) {
+            if (!t.active) return;
+            const __half2 s2 = __half2half2(r.sc);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float4* dst = reinterpret_cast<float4*>(y + (t.row0 + 4 * i + t.rg) * N + t.col);
+            for (int i = 0; i < NP; ++i) {
+                float f[16];
+                dequant16_h(r.d[i], s2, f);
+                float4* dst = reinterpret_cast<float4*>(y + row_of<TW>(t, i) * N + t.col);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            float4 o;
-            o.x = __half2float(deq16(q_at(raw[i], 4 * k + 0), sc));
-            o.y = __half2float(deq16(q_at(raw[i], 4 * k + 1), sc));
-            o.z = __half2float(deq16(q_at(raw[i], 4 * k + 2), sc));
-            o.w = __half2float(deq16(q_at(raw[i], 4 * k + 3), sc));
-            dst[k] = o;
-        }
-    }
+                for (int k = 0; k < 4; ++k) dst[k] = make_float4(f[4 * k], f[4 * k + 1], f[4 * k + 2], f[4 * k + 3]);
+            }
+        });
 }
 
 // =========================================================================================================
 // transpose: y[N, M] = x[M, N]^T (int8)
 // =========================================================================================================
-__global__ void __launch_bounds__(THREADS) transpose_kernel(const int8_t* __restrict__ x, int64_t M, int64_t N, int8_t* __restrict__ y) {
-    __shared__ __align__(16) uint32_t smem_tiles[WARPS * 32 * 32];
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    uint32_t* tile_words = smem_tiles + (threadIdx.x >> 5) * 1024;
-    int4 raw[8];
-    load_q(x, t, N, raw);
+template <int TW>
+__global__ void __launch_bounds__(THREADS, 2)
+transpose_kernel(const int8_t* __restrict__ x, int64_t M, int64_t N, int8_t* __restrict__ y) {
+    constexpr int NP = Geo<TW>::NP;
+    using Raw = RawQ<NP>;
+    __shared__ __align__(16) uint32_t smem_tiles[WARPS * 8 * TW];
+    uint32_t* tile_words = smem_tiles + (threadIdx.x >> 5) * 8 * TW;
+    for_each_tile<TW, Raw, true>(
+        M, N, [&](const Tile& t, Raw& r) { load_rows<TW>(x, t, N, r.d); },
+        [&](const Tile& t, Raw& r) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) *reinterpret_cast<int4*>(tile_words + (4 * i + t.rg) * 32 + t.cc * 4) = raw[i];
-    __syncwarp();
-    store_tile_transposed(tile_words, t, M, N, y);
+            for (int i = 0; i < NP; ++i)
+                *reinterpret_cast<int4*>(tile_words + (i * Geo<TW>::RPP + t.rg) * (TW / 4) + t.cc * 4) = r.d[i];
+            __syncwarp();
+            store_tile_transposed<TW>(tile_words, t, M, N, y);
+            __syncwarp();
+        });
 }
 
 // =========================================================================================================
-// GELU forward: x = fp16(q*s); y = x * (1 + erf(x / sqrt(2))) / 2; block quantise with amax + 5e-5
+// GELU.  Phi(x) = 0.5 * (1 + erf(x / sqrt(2))) is evaluated as 1 - 0.5*erfc(u) (x >= 0) or 0.5*erfc(u) (x < 0), u = |x|/sqrt(2),
+// erfc(u) = P(1/(1+p*u)) * exp(-x^2/2)  (Abramowitz-Stegun 7.1.26, absolute error <= 1.5e-7: orders of magnitude below one
+// quantisation step of the output, and the exponential is shared with the density term of the backward pass).
 // =========================================================================================================
-__device__ __forceinline__ float div_const(float a, float b, float inv_b) {
-    // exact RN(a / b) for a compile-time divisor whose correctly rounded reciprocal is inv_b
-    const float q0 = __fmul_rn(a, inv_b);
-    const float r = __fmaf_rn(-b, q0, a);
-    return __fmaf_rn(r, inv_b, q0);
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
 }
-#define JF_SQRT2 0x1.6a09e6p+0f        /* RN(sqrt(2)) in fp32        */
-#define JF_INV_SQRT2 0x1.6a09e6p-1f    /* RN(1 / JF_SQRT2)           */
-#define JF_SQRT2PI 0x1.40d932p+1f      /* RN(sqrt(RN(2*pi))) in fp32 */
-#define JF_INV_SQRT2PI 0x1.988454p-2f  /* RN(1 / JF_SQRT2PI)         */
-
-__global__ void __launch_bounds__(THREADS) gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, int64_t M,
-                                                           int64_t N, int8_t* __restrict__ qy, __half* __restrict__ sy) {
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    int4 raw[8];
-    load_q(qx, t, N, raw);
-    const float sc = load_scale(sx, t, N);
-    float v[8][16];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float x = __half2float(deq16(q_at(raw[i], j), sc));
-            const float e = erff(div_const(x, JF_SQRT2, JF_INV_SQRT2));
-            const float cdf = __fmul_rn(__fadd_rn(1.0f, e), 0.5f);
-            v[i][j] = __fmul_rn(cdf, x);
-        }
-    const float amax = __fadd_rn(block_max(absmax_8x16(v)), 5e-5f);
-    const float scale32 = __fdiv_rn(amax, 127.0f);
-    SrCfg sr{0, nullptr, 0, 0};
-    emit_quantized<false, false>(v, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+// returns Phi(x); *ex receives exp(-x^2/2)
+__device__ __forceinline__ float gelu_cdf(float x, float* ex) {
+    const float u = __fmul_rn(fabsf(x), 0.70710678118654752f);
+    const float tt = rcp_approx(__fmaf_rn(0.3275911f, u, 1.0f));
+    float pq = __fmaf_rn(1.061405429f, tt, -1.453152027f);
+    pq = __fmaf_rn(pq, tt, 1.421413741f);
+    pq = __fmaf_rn(pq, tt, -0.284496736f);
+    pq = __fmaf_rn(pq, tt, 0.254829592f);
+    const float e = __expf(__fmul_rn(__fmul_rn(x, x), -0.5f));
+    *ex = e;
+    const float half_erfc = __fmul_rn(__fmul_rn(pq, tt), __fmul_rn(0.5f, e));
+    return x < 0.f ? half_erfc : __fsub_rn(1.0f, half_erfc);
 }
 
-// =========================================================================================================
-// GELU backward: x = q*s, g = qg*sg in fp32; d = (Phi(x) + x*phi(x)) * g; block quantise (+SR)
-// =========================================================================================================
-__global__ void __launch_bounds__(THREADS) gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx,
-                                                           const int8_t* __restrict__ qg, const __half* __restrict__ sg, int64_t M,
-                                                           int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd, SrCfg sr) {
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    int4 rx[8], rg_[8];
-    load_q(qx, t, N, rx);
-    load_q(qg, t, N, rg_);
-    const float scx = load_scale(sx, t, N), scg = load_scale(sg, t, N);
-    float v[8][16];
+// forward: x = fp16(q*s); y = x * Phi(x); block quantise with amax + 5e-5
+template <int TW>
+__global__ void __launch_bounds__(THREADS, TW == 64 ? 2 : 1)
+gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, int64_t M, int64_t N, int8_t* __restrict__ qy,
+                __half* __restrict__ sy) {
+    constexpr int NP = Geo<TW>::NP;
+    using Raw = RawQ<NP>;
+    for_each_tile<TW, Raw, true>(
+        M, N,
+        [&](const Tile& t, Raw& r) {
+            load_rows<TW>(qx, t, N, r.d);
+            r.sc = load_scale16(sx, t, N);
+        },
+        [&](const Tile& t, Raw& r) {
+            const __half2 s2 = __half2half2(r.sc);
+            float v[NP][16];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < NP; ++i) {
+                float f[16];
+                dequant16_h(r.d[i], s2, f);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float x = __fmul_rn((float)q_at(rx[i], j), scx);
-            const float g = __fmul_rn((float)q_at(rg_[i], j), scg);
-            const float cdf = __fmul_rn(0.5f, __fadd_rn(1.0f, erff(div_const(x, JF_SQRT2, JF_INV_SQRT2))));
-            const float ex = expf(__fmul_rn(-__fmul_rn(x, x), 0.5f));
-            const float pdf = __fmul_rn(div_const(x, JF_SQRT2PI, JF_INV_SQRT2PI), ex);
-            v[i][j] = __fmul_rn(__fadd_rn(cdf, pdf), g);
-        }
-    const float amax = block_max(absmax_8x16(v));
-    const float scale32 = __fdiv_rn(amax, 127.0f);
-    emit_quantized<false, false>(v, scale32, t, M, N, qd, sd, sr, nullptr, nullptr);
+                for (int j = 0; j < 16; ++j) {
+                    float e;
+                    v[i][j] = __fmul_rn(gelu_cdf(f[j], &e), f[j]);
+                }
+            }
+            const float amax = __fadd_rn(block_max<TW>(absmax_tile<NP>(v)), 5e-5f);
+            const float scale32 = __fdiv_rn(amax, 127.0f);
+            SrCfg sr{nullptr, 0, 0};
+            emit_quantized<TW, false, false, false>([&](int i, float (&a)[16]) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) a[j] = v[i][j];
+            }, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+        });
+}
+
+// backward: x = q*s, g = qg*sg in fp32; d = (Phi(x) + x*phi(x)) * g; block quantise (+SR)
+template <int TW, bool SR>
+__global__ void __launch_bounds__(THREADS, TW == 64 ? 2 : 1)
+gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
+                const __half* __restrict__ sg, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd, SrCfg sr) {
+    constexpr int NP = Geo<TW>::NP;
+    using Raw = RawQ2<NP>;
+    for_each_tile<TW, Raw, true>(
+        M, N,
+        [&](const Tile& t, Raw& r) {
+            load_rows<TW>(qx, t, N, r.a);
+            load_rows<TW>(qg, t, N, r.b);
+            r.sa = load_scale16(sx, t, N);
+            r.sb = load_scale16(sg, t, N);
+        },
+        [&](const Tile& t, Raw& r) {
+            const float scx = __half2float(r.sa), scg = __half2float(r.sb);
+            float v[NP][16];
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                float fx[16], fg[16];
+                unpack16(r.a[i], fx);
+                unpack16(r.b[i], fg);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float x = __fmul_rn(fx[j], scx);
+                    const float g = __fmul_rn(fg[j], scg);
+                    float e;
+                    const float cdf = gelu_cdf(x, &e);
+                    const float pdf = __fmul_rn(__fmul_rn(x, 0.3989422804014327f), e);
+                    v[i][j] = __fmul_rn(__fadd_rn(cdf, pdf), g);
+                }
+            }
+            const float scale32 = __fdiv_rn(block_max<TW>(absmax_tile<NP>(v)), 127.0f);
+            emit_quantized<TW, false, SR, false>([&](int i, float (&a)[16]) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) a[j] = v[i][j];
+            }, scale32, t, M, N, qd, sd, sr, nullptr, nullptr);
+        });
 }
 
 // =========================================================================================================
 // LayerNorm forward: y = ((fp16(q*s) - mean) * rstd) * gamma; statistics are inputs
 // =========================================================================================================
-__global__ void __launch_bounds__(THREADS) ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx,
-                                                         const float* __restrict__ gamma, const float* __restrict__ mean,
-                                                         const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qy,
-                                                         __half* __restrict__ sy) {
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    int4 raw[8];
-    load_q(qx, t, N, raw);
-    const float sc = load_scale(sx, t, N);
-    float gm[16];
-    if (t.active) {
-        Load16<float>::load(gamma + t.col, gm);
-    } else {
+template <int TW>
+__global__ void __launch_bounds__(THREADS, TW == 64 ? 2 : 1)
+ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const float* __restrict__ gamma,
+              const float* __restrict__ mean, const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qy,
+              __half* __restrict__ sy) {
+    constexpr int NP = Geo<TW>::NP;
+    using Raw = RawQ<NP>;
+    for_each_tile<TW, Raw, true>(
+        M, N,
+        [&](const Tile& t, Raw& r) {
+            load_rows<TW>(qx, t, N, r.d);
+            r.sc = load_scale16(sx, t, N);
+        },
+        [&](const Tile& t, Raw& r) {
+            const __half2 s2 = __half2half2(r.sc);
+            float gm[16];
+            if (t.active) {
+                Load16<float>::load(gamma + t.col, gm);
+            } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) gm[j] = 0.f;
-    }
-    float v[8][16];
+                for (int j = 0; j < 16; ++j) gm[j] = 0.f;
+            }
+            float v[NP][16];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int64_t row = t.row0 + 4 * i + t.rg;
-        const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+            for (int i = 0; i < NP; ++i) {
+                const int64_t row = row_of<TW>(t, i);
+                const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+                float f[16];
+                dequant16_h(r.d[i], s2, f);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float x = __half2float(deq16(q_at(raw[i], j), sc));
-            const float xhat = __fmul_rn(__fsub_rn(x, mu), rs);
-            v[i][j] = __fadd_rn(__fmul_rn(xhat, gm[j]), 0.0f);
-        }
-    }
-    const float amax = block_max(absmax_8x16(v));
-    const float scale32 = __fdiv_rn(amax, 127.0f);
-    SrCfg sr{0, nullptr, 0, 0};
-    emit_quantized<false, false>(v, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+                for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(__fmul_rn(__fsub_rn(f[j], mu), rs), gm[j]);
+            }
+            const float scale32 = __fdiv_rn(block_max<TW>(absmax_tile<NP>(v)), 127.0f);
+            SrCfg sr{nullptr, 0, 0};
+            emit_quantized<TW, false, false, false>([&](int i, float (&a)[16]) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) a[j] = v[i][j];
+            }, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+        });
 }
 
 // =========================================================================================================
-// LayerNorm backward (dx and per-32-row partial dgamma), row reductions over the tile's 128-column slab
+// LayerNorm backward (dx and per-32-row partial dgamma), row reductions over the tile's 128-column slab.
+// Rounding points of the reference: mean, rstd, x, dy, xhat in fp16; c1, c2 and the dx expression in fp32; dx -> fp16.
 // =========================================================================================================
-__global__ void __launch_bounds__(THREADS) ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx,
-                                                         const int8_t* __restrict__ qg, const __half* __restrict__ sg,
-                                                         const float* __restrict__ gamma, const float* __restrict__ mean,
-                                                         const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qd,
-                                                         __half* __restrict__ sd, float* __restrict__ dw_partial, SrCfg sr) {
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    int4 rx[8], rgr[8];
-    load_q(qx, t, N, rx);
-    load_q(qg, t, N, rgr);
-    const float scx = load_scale(sx, t, N), scg = load_scale(sg, t, N);
+template <bool SR>
+__global__ void __launch_bounds__(THREADS, 1)
+ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
+              const __half* __restrict__ sg, const float* __restrict__ gamma, const float* __restrict__ mean,
+              const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd,
+              float* __restrict__ dw_partial, SrCfg sr) {
+    constexpr int TW = 128, NP = Geo<TW>::NP;
+    const int64_t tiles_n_ = (N + TW - 1) / TW;
+    const int64_t tile_ = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (tile_ >= (M / QB) * tiles_n_) return;
+    const Tile t = make_tile<TW>(tile_, tiles_n_, N);
+    int4 rx[NP], rgr[NP];
+    load_rows<TW>(qx, t, N, rx);
+    load_rows<TW>(qg, t, N, rgr);
+    const __half2 sx2 = load_scale_h2(sx, t, N), sg2 = load_scale_h2(sg, t, N);
     float gm[16];
     if (t.active) {
         Load16<float>::load(gamma + t.col, gm);
@@ -363,59 +588,55 @@ __global__ void __launch_bounds__(THREADS) ln_bwd_kernel(const int8_t* __restric
 #pragma unroll
         for (int j = 0; j < 16; ++j) gm[j] = 0.f;
     }
-    const float invN_den = (float)N;
-    float v[8][16];     // dx, rounded to fp16 and widened
-    float dwp[16];      // partial dgamma over this lane's 8 rows
+    const float n_f = (float)N;
+    float v[NP][16];    // dx, rounded to fp16 and widened
+    float dwp[16];      // partial dgamma over this lane's rows
 #pragma unroll
     for (int j = 0; j < 16; ++j) dwp[j] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int64_t row = t.row0 + 4 * i + t.rg;
-        const __half mu16 = __float2half_rn(__ldg(mean + row));
+    for (int i = 0; i < NP; ++i) {
+        const int64_t row = row_of<TW>(t, i);
+        const __half2 mu2 = __half2half2(__float2half_rn(__ldg(mean + row)));
         const __half rs16 = __float2half_rn(__ldg(rstd + row));
+        const __half2 rs2 = __half2half2(rs16);
         const float rs = __half2float(rs16);
-        float xh[16], wdy[16];
+        float fx[16], fg[16], xh[16], wdy[16];
+        unpack16(rx[i], fx);
+        unpack16(rgr[i], fg);
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const __half x16 = deq16(q_at(rx[i], j), scx);
-            const __half dy16 = deq16(q_at(rgr[i], j), scg);
-            const __half xhat16 = __hmul(__hsub(x16, mu16), rs16);
-            xh[j] = __half2float(xhat16);
-            const float dy = __half2float(dy16);
-            wdy[j] = __fmul_rn(gm[j], dy);
-            s1 = __fadd_rn(s1, __fmul_rn(xh[j], wdy[j]));
-            s2 = __fadd_rn(s2, wdy[j]);
-            dwp[j] = __fadd_rn(dwp[j], __half2float(__hmul(dy16, xhat16)));
+        for (int j = 0; j < 8; ++j) {
+            const __half2 x16 = __hmul2_rn(__floats2half2_rn(fx[2 * j], fx[2 * j + 1]), sx2);
+            const __half2 dy16 = __hmul2_rn(__floats2half2_rn(fg[2 * j], fg[2 * j + 1]), sg2);
+            const __half2 xhat16 = __hmul2_rn(__hsub2_rn(x16, mu2), rs2);
+            const float2 xf = __half22float2(xhat16), dyf = __half22float2(dy16), pr = __half22float2(__hmul2_rn(dy16, xhat16));
+            xh[2 * j] = xf.x; xh[2 * j + 1] = xf.y;
+            wdy[2 * j] = __fmul_rn(gm[2 * j], dyf.x); wdy[2 * j + 1] = __fmul_rn(gm[2 * j + 1], dyf.y);
+            s1 = __fadd_rn(__fadd_rn(s1, __fmul_rn(xh[2 * j], wdy[2 * j])), __fmul_rn(xh[2 * j + 1], wdy[2 * j + 1]));
+            s2 = __fadd_rn(__fadd_rn(s2, wdy[2 * j]), wdy[2 * j + 1]);
+            dwp[2 * j] = __fadd_rn(dwp[2 * j], pr.x); dwp[2 * j + 1] = __fadd_rn(dwp[2 * j + 1], pr.y);
         }
-        // row sums over the 128-column slab: the 8 lanes sharing rg
-        s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, 1)); s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 1));
-        s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, 2)); s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 2));
-        s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, 4)); s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 4));
-        const float c1 = __fdiv_rn(s1, invN_den), c2 = __fdiv_rn(s2, invN_den);
+        const float c1 = __fdiv_rn(row_sum<TW>(s1), n_f), c2 = __fdiv_rn(row_sum<TW>(s2), n_f);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float tt = __fadd_rn(__fmul_rn(xh[j], c1), c2);
-            const float dx = __fmul_rn(__fsub_rn(wdy[j], tt), rs);
-            v[i][j] = __half2float(__float2half_rn(dx));
+            v[i][j] = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(wdy[j], tt), rs)));
         }
     }
-    // partial dgamma: reduce the four row groups, lanes with rg == 0 write 16 columns
+    // partial dgamma: reduce the row groups, lanes with rg == 0 write 16 columns
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        float a = dwp[j];
-        a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 8));
-        a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 16));
-        dwp[j] = a;
-    }
+    for (int j = 0; j < 16; ++j) dwp[j] = col_sum<TW>(dwp[j]);
     if (t.active && t.rg == 0) {
         float4* dst = reinterpret_cast<float4*>(dw_partial + t.tm * N + t.col);
 #pragma unroll
         for (int k = 0; k < 4; ++k) dst[k] = make_float4(dwp[4 * k], dwp[4 * k + 1], dwp[4 * k + 2], dwp[4 * k + 3]);
     }
-    const float amax = block_max(absmax_8x16(v));   // exactly representable in fp16
+    const float amax = block_max<TW>(absmax_tile<NP>(v));   // exactly representable in fp16
     const float scale32 = __fdiv_rn(amax, 127.0f);
-    emit_quantized<false, false>(v, scale32, t, M, N, qd, sd, sr, nullptr, nullptr);
+    emit_quantized<TW, false, SR, false>([&](int i, float (&a)[16]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) a[j] = v[i][j];
+    }, scale32, t, M, N, qd, sd, sr, nullptr, nullptr);
 }
 
 // dgamma[n] = sum over the M/32 partial rows, ascending
@@ -430,35 +651,39 @@ __global__ void ln_bwd_dw_kernel(const float* __restrict__ partial, int64_t rows
 // =========================================================================================================
 // residual add (+ optional row statistics): y = x1 + q2*s2 (fp32); store y; block quantise y by truncation
 // =========================================================================================================
-template <typename T, bool MEANVAR>
-__global__ void __launch_bounds__(THREADS) add_kernel(const T* __restrict__ x1, const int8_t* __restrict__ q2,
-                                                      const __half* __restrict__ s2, int64_t M, int64_t N, float* __restrict__ y1,
-                                                      int8_t* __restrict__ qy, __half* __restrict__ sy, float* __restrict__ part_sum,
-                                                      float* __restrict__ part_sq, SrCfg sr) {
-    Tile t;
-    if (!tile_setup(M, N, t)) return;
-    int4 raw[8];
-    load_q(q2, t, N, raw);
+template <typename T, bool MEANVAR, bool SR>
+__global__ void __launch_bounds__(THREADS, 1)
+add_kernel(const T* __restrict__ x1, const int8_t* __restrict__ q2, const __half* __restrict__ s2, int64_t M, int64_t N,
+           float* __restrict__ y1, int8_t* __restrict__ qy, __half* __restrict__ sy, float* __restrict__ part_sum,
+           float* __restrict__ part_sq, SrCfg sr) {
+    constexpr int TW = 128, NP = Geo<TW>::NP;
+    const int64_t tiles_n_ = (N + TW - 1) / TW;
+    const int64_t tile_ = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (tile_ >= (M / QB) * tiles_n_) return;
+    const Tile t = make_tile<TW>(tile_, tiles_n_, N);
+    int4 raw[NP];
+    load_rows<TW>(q2, t, N, raw);
     const float sc = load_scale(s2, t, N);
-    const int64_t tiles_n = (N + TILE_N - 1) / TILE_N;
-    float v[8][16];
+    const int64_t tiles_n = (N + TW - 1) / TW;
+    float v[NP][16];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int64_t row = t.row0 + 4 * i + t.rg;
+    for (int i = 0; i < NP; ++i) {
         if (t.active) {
-            Load16<T>::load(x1 + row * N + t.col, v[i]);
+            Load16<T>::load(x1 + row_of<TW>(t, i) * N + t.col, v[i]);
         } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
         }
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int64_t row = t.row0 + 4 * i + t.rg;
+    for (int i = 0; i < NP; ++i) {
+        const int64_t row = row_of<TW>(t, i);
+        float f[16];
+        unpack16(raw[i], f);
         float ps = 0.f, pq = 0.f;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const float y = __fadd_rn(v[i][j], __fmul_rn((float)q_at(raw[i], j), sc));
+            const float y = __fadd_rn(v[i][j], __fmul_rn(f[j], sc));
             v[i][j] = y;
             if (MEANVAR) {
                 ps = __fadd_rn(ps, y);
@@ -471,18 +696,20 @@ __global__ void __launch_bounds__(THREADS) add_kernel(const T* __restrict__ x1, 
             for (int k = 0; k < 4; ++k) dst[k] = make_float4(v[i][4 * k], v[i][4 * k + 1], v[i][4 * k + 2], v[i][4 * k + 3]);
         }
         if (MEANVAR) {
-            ps = __fadd_rn(ps, __shfl_xor_sync(0xffffffffu, ps, 1)); pq = __fadd_rn(pq, __shfl_xor_sync(0xffffffffu, pq, 1));
-            ps = __fadd_rn(ps, __shfl_xor_sync(0xffffffffu, ps, 2)); pq = __fadd_rn(pq, __shfl_xor_sync(0xffffffffu, pq, 2));
-            ps = __fadd_rn(ps, __shfl_xor_sync(0xffffffffu, ps, 4)); pq = __fadd_rn(pq, __shfl_xor_sync(0xffffffffu, pq, 4));
+            ps = row_sum<TW>(ps);
+            pq = row_sum<TW>(pq);
             if (t.cc == 0) {
                 part_sum[row * tiles_n + t.tn] = ps;
                 part_sq[row * tiles_n + t.tn] = pq;
             }
         }
     }
-    const float amax = block_max(absmax_8x16(v));
+    const float amax = block_max<TW>(absmax_tile<NP>(v));
     const float scale32 = __fdiv_rn(amax, 127.0f);
-    emit_quantized<true, false>(v, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+    emit_quantized<TW, true, SR, false>([&](int i, float (&a)[16]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) a[j] = v[i][j];
+    }, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
 }
 
 // mean = sum/N; rstd = 1/sqrt(sumsq/N - mean^2)
@@ -502,6 +729,8 @@ __global__ void meanvar_finish_kernel(const float* __restrict__ part_sum, const 
     rstd[row] = __fdiv_rn(1.0f, __fsqrt_rn(var));
 }
 
+
+
 }  // namespace jf
 
 // =========================================================================================================
@@ -519,6 +748,51 @@ using namespace jf;
     } while (0)
 
 static inline int check_mn(int64_t M, int64_t N) { return (mult32(M) && mult32(N)) ? JF_OK : JF_ERR_SHAPE; }
+
+// CTAs of a persistent launch: two per SM (the streaming kernels fit two 8-warp CTAs per SM; one that fits only one simply runs
+// its second half afterwards).
+static int persistent_ctas() {
+    static const int n = [] {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        return 2 * sms;
+    }();
+    return n;
+}
+
+// Tile width of the single-input streaming kernels: 64 by default; JF_NL_TW=128 selects the wide tile (tuning only).
+static int narrow_tw() {
+    static const int tw = [] { const char* e = getenv("JF_NL_TW"); return (e && atoi(e) == 128) ? 128 : 64; }();
+    return tw;
+}
+#define JF_TW_DISPATCH(CALL64, CALL128) \
+    do {                                \
+        if (narrow_tw() == 64) { CALL64; } else { CALL128; } \
+    } while (0)
+
+template <typename T, int TW>
+static void launch_quantize(const void* x, int64_t M, int64_t N, int8_t* q, __half* s, int8_t* qt, bool stochastic, SrCfg sr,
+                            cudaStream_t st) {
+    const unsigned grid = grid_for<TW>(M, N, persistent_ctas());
+    const T* xp = (const T*)x;
+    if (qt) {
+        if (stochastic) quantize_kernel<T, TW, true, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
+        else quantize_kernel<T, TW, false, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
+    } else {
+        if (stochastic) quantize_kernel<T, TW, true, false><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, nullptr, sr);
+        else quantize_kernel<T, TW, false, false><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, nullptr, sr);
+    }
+}
+
+template <typename T>
+static void launch_add(const void* x1, const int8_t* q2, const __half* s2, int64_t M, int64_t N, float* y1, int8_t* qy, __half* sy,
+                       float* ps, float* pq, bool meanvar, bool stochastic, SrCfg sr, cudaStream_t st) {
+    const unsigned grid = grid_for<128>(M, N);
+    const T* xp = (const T*)x1;
+    if (meanvar) add_kernel<T, true, false><<<grid, THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
+    else if (stochastic) add_kernel<T, false, true><<<grid, THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
+    else add_kernel<T, false, false><<<grid, THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
+}
 
 extern "C" {
 
@@ -546,19 +820,15 @@ int jf_int8_quantize(const void* x, int x_dtype, int64_t M, int64_t N, int8_t* q
     if (qt) JF_REQUIRE_ALIGNED(qt);
     if (noise) JF_REQUIRE_ALIGNED(noise);
     cudaStream_t st = (cudaStream_t)stream;
-    SrCfg sr{stochastic, noise, seed, offset};
-    const unsigned grid = grid_for(M, N);
+    SrCfg sr{noise, seed, offset};
     __half* sh = (__half*)s;
-#define JF_LAUNCH_Q(T)                                                                                   \
-    if (qt) quantize_kernel<T, true><<<grid, THREADS, 0, st>>>((const T*)x, M, N, q, sh, qt, sr);        \
-    else quantize_kernel<T, false><<<grid, THREADS, 0, st>>>((const T*)x, M, N, q, sh, nullptr, sr);
+    const bool sto = stochastic != 0;
     switch (x_dtype) {
-        case JF_F32: JF_LAUNCH_Q(float) break;
-        case JF_F16: JF_LAUNCH_Q(__half) break;
-        case JF_BF16: JF_LAUNCH_Q(__nv_bfloat16) break;
+        case JF_F32: JF_TW_DISPATCH((launch_quantize<float, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<float, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
+        case JF_F16: JF_TW_DISPATCH((launch_quantize<__half, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__half, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
+        case JF_BF16: JF_TW_DISPATCH((launch_quantize<__nv_bfloat16, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__nv_bfloat16, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
         default: return JF_ERR_DTYPE;
     }
-#undef JF_LAUNCH_Q
     return check_launch();
 }
 
@@ -566,7 +836,9 @@ int jf_int8_dequantize(const int8_t* q, const void* s, int64_t M, int64_t N, flo
     JF_REQUIRE_PTR(q); JF_REQUIRE_PTR(s); JF_REQUIRE_PTR(y);
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(q); JF_REQUIRE_ALIGNED(y);
-    dequantize_kernel<<<grid_for(M, N), THREADS, 0, (cudaStream_t)stream>>>(q, (const __half*)s, M, N, y);
+    cudaStream_t st = (cudaStream_t)stream;
+    JF_TW_DISPATCH((dequantize_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(q, (const __half*)s, M, N, y)),
+                   (dequantize_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(q, (const __half*)s, M, N, y)));
     return check_launch();
 }
 
@@ -574,7 +846,9 @@ int jf_int8_transpose(const int8_t* x, int64_t M, int64_t N, int8_t* y, void* st
     JF_REQUIRE_PTR(x); JF_REQUIRE_PTR(y);
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(x); JF_REQUIRE_ALIGNED(y);
-    transpose_kernel<<<grid_for(M, N), THREADS, 0, (cudaStream_t)stream>>>(x, M, N, y);
+    cudaStream_t st = (cudaStream_t)stream;
+    JF_TW_DISPATCH((transpose_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(x, M, N, y)),
+                   (transpose_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(x, M, N, y)));
     return check_launch();
 }
 
@@ -582,7 +856,9 @@ int jf_int8_gelu_forward(const int8_t* qx, const void* sx, int64_t M, int64_t N,
     JF_REQUIRE_PTR(qx); JF_REQUIRE_PTR(sx); JF_REQUIRE_PTR(qy); JF_REQUIRE_PTR(sy);
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qy);
-    gelu_fwd_kernel<<<grid_for(M, N), THREADS, 0, (cudaStream_t)stream>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy);
+    cudaStream_t st = (cudaStream_t)stream;
+    JF_TW_DISPATCH((gelu_fwd_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy)),
+                   (gelu_fwd_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy)));
     return check_launch();
 }
 
@@ -592,9 +868,16 @@ int jf_int8_gelu_backward(const int8_t* qx, const void* sx, const int8_t* qg, co
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qg); JF_REQUIRE_ALIGNED(qd);
     if (noise) JF_REQUIRE_ALIGNED(noise);
-    SrCfg sr{stochastic, noise, seed, offset};
-    gelu_bwd_kernel<<<grid_for(M, N), THREADS, 0, (cudaStream_t)stream>>>(qx, (const __half*)sx, qg, (const __half*)sg, M, N, qd,
-                                                                          (__half*)sd, sr);
+    SrCfg sr{noise, seed, offset};
+    cudaStream_t st = (cudaStream_t)stream;
+    const __half* sxh = (const __half*)sx; const __half* sgh = (const __half*)sg; __half* sdh = (__half*)sd;
+    if (stochastic) {
+        JF_TW_DISPATCH((gelu_bwd_kernel<64, true><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)),
+                       (gelu_bwd_kernel<128, true><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)));
+    } else {
+        JF_TW_DISPATCH((gelu_bwd_kernel<64, false><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)),
+                       (gelu_bwd_kernel<128, false><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)));
+    }
     return check_launch();
 }
 
@@ -604,8 +887,9 @@ int jf_int8_layernorm_forward(const int8_t* qx, const void* sx, const float* gam
     JF_REQUIRE_PTR(qy); JF_REQUIRE_PTR(sy);
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qy); JF_REQUIRE_ALIGNED(gamma);
-    ln_fwd_kernel<<<grid_for(M, N), THREADS, 0, (cudaStream_t)stream>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy,
-                                                                        (__half*)sy);
+    cudaStream_t st = (cudaStream_t)stream;
+    JF_TW_DISPATCH((ln_fwd_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy, (__half*)sy)),
+                   (ln_fwd_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy, (__half*)sy)));
     return check_launch();
 }
 
@@ -617,26 +901,29 @@ int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* q
     JF_REQUIRE_PTR(mean); JF_REQUIRE_PTR(rstd); JF_REQUIRE_PTR(qd); JF_REQUIRE_PTR(sd); JF_REQUIRE_PTR(dgamma);
     JF_REQUIRE_PTR(scratch);
     if (int e = check_mn(M, N)) return e;
-    if (slab != TILE_N) return JF_ERR_ARG;         // only the reference's 128-column slab is implemented
-    if (N % TILE_N != 0) return JF_ERR_SHAPE;
+    if (slab != 128) return JF_ERR_ARG;         // only the reference's 128-column slab is implemented
+    if (N % 128 != 0) return JF_ERR_SHAPE;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qg); JF_REQUIRE_ALIGNED(qd); JF_REQUIRE_ALIGNED(gamma); JF_REQUIRE_ALIGNED(scratch);
     if (noise) JF_REQUIRE_ALIGNED(noise);
     cudaStream_t st = (cudaStream_t)stream;
-    SrCfg sr{stochastic, noise, seed, offset};
-    ln_bwd_kernel<<<grid_for(M, N), THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd,
-                                                      (__half*)sd, scratch, sr);
+    SrCfg sr{noise, seed, offset};
+    const unsigned grid = grid_for<128>(M, N);
+    if (stochastic)
+        ln_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
+    else
+        ln_bwd_kernel<false><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
     if (int e = check_launch()) return e;
     ln_bwd_dw_kernel<<<(unsigned)((N + 127) / 128), 128, 0, st>>>(scratch, M / QB, N, dgamma);
     return check_launch();
 }
 
 static int add_impl(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1, int8_t* qy,
-                    void* sy, float* mean, float* rstd, float* scratch, bool meanvar, SrCfg sr, cudaStream_t st) {
+                    void* sy, float* mean, float* rstd, float* scratch, bool meanvar, bool stochastic, SrCfg sr, cudaStream_t st) {
     JF_REQUIRE_PTR(x1); JF_REQUIRE_PTR(q2); JF_REQUIRE_PTR(s2); JF_REQUIRE_PTR(y1); JF_REQUIRE_PTR(qy); JF_REQUIRE_PTR(sy);
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(x1); JF_REQUIRE_ALIGNED(q2); JF_REQUIRE_ALIGNED(y1); JF_REQUIRE_ALIGNED(qy);
     if (sr.noise) JF_REQUIRE_ALIGNED(sr.noise);
-    const int64_t tiles_n = (N + TILE_N - 1) / TILE_N;
+    const int64_t tiles_n = (N + 127) / 128;
     float* ps = nullptr;
     float* pq = nullptr;
     if (meanvar) {
@@ -644,19 +931,14 @@ static int add_impl(const void* x1, int x1_dtype, const int8_t* q2, const void* 
         ps = scratch;
         pq = scratch + M * tiles_n;
     }
-    const unsigned grid = grid_for(M, N);
     const __half* s2h = (const __half*)s2;
     __half* syh = (__half*)sy;
-#define JF_LAUNCH_ADD(T)                                                                                        \
-    if (meanvar) add_kernel<T, true><<<grid, THREADS, 0, st>>>((const T*)x1, q2, s2h, M, N, y1, qy, syh, ps, pq, sr); \
-    else add_kernel<T, false><<<grid, THREADS, 0, st>>>((const T*)x1, q2, s2h, M, N, y1, qy, syh, ps, pq, sr);
     switch (x1_dtype) {
-        case JF_F32: JF_LAUNCH_ADD(float) break;
-        case JF_F16: JF_LAUNCH_ADD(__half) break;
-        case JF_BF16: JF_LAUNCH_ADD(__nv_bfloat16) break;
+        case JF_F32: launch_add<float>(x1, q2, s2h, M, N, y1, qy, syh, ps, pq, meanvar, stochastic, sr, st); break;
+        case JF_F16: launch_add<__half>(x1, q2, s2h, M, N, y1, qy, syh, ps, pq, meanvar, stochastic, sr, st); break;
+        case JF_BF16: launch_add<__nv_bfloat16>(x1, q2, s2h, M, N, y1, qy, syh, ps, pq, meanvar, stochastic, sr, st); break;
         default: return JF_ERR_DTYPE;
     }
-#undef JF_LAUNCH_ADD
     if (int e = check_launch()) return e;
     if (meanvar) {
         meanvar_finish_kernel<<<(unsigned)((M + 127) / 128), 128, 0, st>>>(ps, pq, M, tiles_n, N, mean, rstd);
@@ -667,14 +949,15 @@ static int add_impl(const void* x1, int x1_dtype, const int8_t* q2, const void* 
 
 int jf_int8_add(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1, int8_t* qy, void* sy,
                 int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream) {
-    SrCfg sr{stochastic, noise, seed, offset};
-    return add_impl(x1, x1_dtype, q2, s2, M, N, y1, qy, sy, nullptr, nullptr, nullptr, false, sr, (cudaStream_t)stream);
+    SrCfg sr{noise, seed, offset};
+    return add_impl(x1, x1_dtype, q2, s2, M, N, y1, qy, sy, nullptr, nullptr, nullptr, false, stochastic != 0, sr, (cudaStream_t)stream);
 }
 
 int jf_int8_add_meanvar(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1, int8_t* qy,
                         void* sy, float* mean, float* rstd, float* scratch, void* stream) {
-    SrCfg sr{0, nullptr, 0, 0};
-    return add_impl(x1, x1_dtype, q2, s2, M, N, y1, qy, sy, mean, rstd, scratch, true, sr, (cudaStream_t)stream);
+    SrCfg sr{nullptr, 0, 0};
+    return add_impl(x1, x1_dtype, q2, s2, M, N, y1, qy, sy, mean, rstd, scratch, true, false, sr, (cudaStream_t)stream);
 }
 
 }  // extern "C"
+

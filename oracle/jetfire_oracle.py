@@ -102,19 +102,19 @@ def philox4x32_10(c0, c1, c2, c3, k0, k1):
 
 
 def sr_noise(M, N, seed, offset):
-    """Noise in (-0.5, 0.5) for element (row, col) of an [M, N] tensor.
+    """Noise in [-0.5, 0.5) for element (row, col) of an [M, N] tensor, as the CUDA kernels generate it.
 
-    Element e = row*N + col uses word (e % 4) of Philox4x32-10 with key = (seed_lo, seed_hi) and
-    counter = (g_lo, g_hi, offset_lo, offset_hi), g = e // 4.  noise = ((w >> 9) - 2**22 + 0.5) * 2**-23,
-    exact in fp32.
+    One Philox4x32-10 call serves 8 consecutive elements: group g = e // 8 of element e = row*N + col, key = (seed_lo, seed_hi),
+    counter = (g_lo, g_hi, offset_lo, offset_hi); element e takes the 16-bit half (e & 1) of word (e >> 1) & 3 and
+    noise = h * 2**-16 - 0.5 (a multiple of 2**-16, exact in fp32).
     """
     total = M * N
-    g = np.arange((total + 3) // 4, dtype=np.uint64)
+    g = np.arange((total + 7) // 8, dtype=np.uint64)
     w = philox4x32_10(g & _MASK32, g >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
                       np.uint64((offset >> 32) & 0xFFFFFFFF), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
-    words = np.stack(w, axis=1).reshape(-1)[:total]
-    k = (words >> np.uint32(9)).astype(np.int64) - (1 << 22)
-    return ((k.astype(np.float64) + 0.5) * 2.0 ** -23).astype(f32).reshape(M, N)
+    words = np.stack(w, axis=1)                                   # [groups, 4]
+    halves = np.stack([words & np.uint32(0xFFFF), words >> np.uint32(16)], axis=2).reshape(-1)[:total]
+    return (halves.astype(np.float64) * 2.0 ** -16 - 0.5).astype(f32).reshape(M, N)
 
 
 # --------------------------------------------------------------------------------------------
