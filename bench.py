@@ -422,13 +422,83 @@ def run_nonlinear(args):
                       "ops": res}), flush=True)
 
 
+def run_gpt2(args):
+    """GPT-2 INT8 training step (nanoGPT shape, synthetic uniform token ids): forward + backward through the INT8 data flow,
+    gradient all-reduce (DDP over NCCL when n_gpus > 1) and a fused AdamW step.  Prints tokens/s."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from jetfire_int8training_b200 import rng
+    from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
+    if args.model == "xl":
+        cfg, mb = GPTConfig(n_layer=48, n_head=25, n_embd=1600), 8
+    elif args.model == "tiny":
+        cfg, mb = GPTConfig(n_layer=2, n_head=4, n_embd=256, block_size=256, vocab_size=4096), 4
+    else:
+        cfg, mb = GPTConfig(), 12
+    mb = args.micro_batch or mb
+    torch.manual_seed(1337)
+    rng.manual_seed(1337 + rank)
+    model = QGPT(cfg).to(dev)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    decay = [p for p in model.parameters() if p.dim() >= 2]
+    nodecay = [p for p in model.parameters() if p.dim() < 2]
+    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": nodecay, "weight_decay": 0.0}], lr=6e-4,
+                            betas=(0.9, 0.95), fused=True)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    T = cfg.block_size
+
+    def batch():
+        ids = torch.randint(0, cfg.vocab_size, (mb, T + 1), generator=g, device=dev)
+        return ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+
+    def step(x, y):
+        loss = net(x, y)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    losses = []
+    for _ in range(max(3, args.warmup)):
+        losses.append(float(step(*batch())))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        loss = step(*batch())
+    b.record(); torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        tms = torch.tensor([ms], device=dev); dist.all_reduce(tms, op=dist.ReduceOp.MAX); ms = float(tms.item())
+    if rank == 0:
+        toks = world * mb * T * args.steps / (ms * 1e-3)
+        print(json.dumps({"metric": "GPT-2 INT8 train tokens/s", "value": toks, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                          "dtype": "int8 linears/LN/GELU, bf16 attention + LM head, fp32 params", "data": "synthetic",
+                          "config": {"workload": f"GPT-2 {args.model} INT8 training step", "n_layer": cfg.n_layer, "n_embd": cfg.n_embd,
+                                     "micro_batch": mb, "seq_len": T, "params": model.num_params(), "parallelism": f"dp{world}"},
+                          "loss_first": losses[0], "loss_last": float(loss)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear", "gpt2"])
+    ap.add_argument("--model", default="124M", choices=["124M", "xl", "tiny"], help="gpt2 workload: model size")
+    ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the linear workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (kernel tuning runs)")
@@ -441,6 +511,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "nonlinear":
         run_nonlinear(args)
+    elif args.workload == "gpt2":
+        run_gpt2(args)
     else:
         run_ours(args)
 

@@ -73,10 +73,11 @@ def int8_linear_wgrad(X8, SX, G8, SG, out_dtype=torch.float16, split_k=0):
 
 
 def int8_linear_backward(X8_3D, SX16_3D, G8_3D, SG16_3D, G8T, W8, SW16, B, stochastic=True, dgrad_quantize=True, *,
-                         sr_key=None, noise=None, wgrad_split_k=0):
+                         sr_key=None, noise=None, wgrad_split_k=0, wgrad_out_dtype=torch.float16):
     """dX = dY W (block-quantised with stochastic rounding, or dequantised fp16 when dgrad_quantize is False) and
     dW = dY^T X (dense fp16).  Returns (GX8, GSX16, GW) or (GX16, GW), as the reference does.
-    The reference ignores `stochastic` and always rounds stochastically; here stochastic=False rounds to nearest."""
+    The reference ignores `stochastic` and always rounds stochastically; here stochastic=False rounds to nearest.
+    `wgrad_out_dtype=torch.float32` (extra) returns dW in fp32 instead of the reference's fp16."""
     if B != 32:
         raise ValueError("only the 32x32 quantisation block of the reference recipe is implemented")
     if not G8_3D.is_cuda:
@@ -112,7 +113,7 @@ def int8_linear_backward(X8_3D, SX16_3D, G8_3D, SG16_3D, G8T, W8, SW16, B, stoch
         check(L.jf_igemm_dgrad(G8.data_ptr(), W8c.data_ptr(), SG.data_ptr(), SG.stride(0), SG.stride(1), SWc.data_ptr(), SWc.stride(0),
                                SWc.stride(1), M, Cin, Cout, JF_OUT_DEQUANT_F16, None, None, gx16.data_ptr(), st, nz, seed, off,
                                _stream()), "int8_linear_backward(dgrad)")
-    gw = int8_linear_wgrad(X8, SX, G8, SG, torch.float16, wgrad_split_k)
+    gw = int8_linear_wgrad(X8, SX, G8, SG, wgrad_out_dtype, wgrad_split_k)
     if dgrad_quantize:
         return gx8.reshape(gx_shape), gsx.reshape(gs_shape), gw
     return gx16.reshape(gx_shape), gw

@@ -1,0 +1,55 @@
+"""GPU: the GPT-2 harness on top of the INT8 operators (the callers of the hot path): shapes, finite gradients for every
+parameter, agreement of the quantised forward loss with a floating-point evaluation of the same weights, and a falling loss
+when a small model is fitted to one fixed batch."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def float_loss(model, idx, targets):
+    """The same network evaluated in fp32 without quantisation."""
+    cfg = model.cfg
+    B, T = idx.shape
+    x = model.wte(idx) + model.wpe(torch.arange(T, device=idx.device))
+    for b in model.blocks:
+        h = F.layer_norm(x, (cfg.n_embd,), b.ln_1, None, 0.0)
+        q, k, v = F.linear(h, b.c_attn).split(cfg.n_embd, dim=2)
+        hs = cfg.n_embd // cfg.n_head
+        q, k, v = [t.view(B, T, cfg.n_head, hs).transpose(1, 2) for t in (q, k, v)]
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, cfg.n_embd)
+        x = x + F.linear(y, b.c_proj)
+        h = F.layer_norm(x, (cfg.n_embd,), b.ln_2, None, 0.0)
+        x = x + F.linear(F.gelu(F.linear(h, b.c_fc)), b.c_proj2)
+    x = F.layer_norm(x, (cfg.n_embd,), model.ln_f, None, 1e-5)
+    return F.cross_entropy(F.linear(x, model.wte.weight).view(-1, cfg.vocab_size), targets.view(-1))
+
+
+def test_small_gpt2_trains():
+    from jetfire_int8training_b200 import rng
+    from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
+    torch.manual_seed(0)
+    rng.manual_seed(0)
+    cfg = GPTConfig(block_size=64, vocab_size=512, n_layer=2, n_head=4, n_embd=128)
+    model = QGPT(cfg).to(DEV)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (4, 65), generator=g, device=DEV)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    loss = model(x, y)
+    with torch.no_grad():
+        ref = float_loss(model, x, y)
+    assert abs(float(loss) - float(ref)) < 0.05 * float(ref)          # INT8 forward tracks the fp32 network
+    loss.backward()
+    for name, p in model.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all(), name
+        assert p.grad.shape == p.shape and p.grad.dtype == p.dtype
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    first = float(loss)
+    for _ in range(40):
+        opt.zero_grad(set_to_none=True)
+        loss = model(x, y)
+        loss.backward()
+        opt.step()
+    assert float(loss) < 0.7 * first
