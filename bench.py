@@ -316,11 +316,18 @@ def run_ours(args):
                              "peak": peak_tops, "unit": "TOPS", "frac": fwd_tops / peak_tops,
                              "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
                              "frac_of_nominal_4500": fwd_tops / 4500.0, "cublas_int_mm_tops": int_mm_tops,
-                             "avg_launch_ms": fwd_ms, "traffic": None},
+                             "avg_launch_ms": fwd_ms,
+                             # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch, from the ncu capture
+                             # summarised in profiles/linear_8192_launches_and_traffic.md (only valid at that size)
+                             "traffic": NCU_FWD_DRAM_BYTES_8192 if (M, N, K) == (8192, 8192, 8192) else None,
+                             "algorithmic_bytes": M * K + N * K + M * N + 2 * (M * K + N * K + M * N) // 1024},
                 "cpu_baseline": cpu, "gemm_error_flag": err}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+NCU_FWD_DRAM_BYTES_8192 = 331696640 + 58046208
 
 
 def nonlinear_ops(M, N, copies, dev):

@@ -9,6 +9,19 @@
 // accumulators in flight; the floor stayed when TMEM loads, arithmetic and even the TMA loads were removed).
 #pragma once
 
+// Tile rasterisation: tiles are numbered in groups of RASTER_GM tile-rows, M-fastest inside a group, so the ~148 tiles that
+// are in flight together cover about 16 x 9 tiles: 16 A panels + 9 B panels (~26 MB at K = 8192) instead of a whole
+// 64-row-panel column of A, which did not stay in L2 (ncu: 1.12 GB of DRAM traffic per 8192^3 launch against 0.2 GB algorithmic).
+constexpr int RASTER_GM = 16;
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
+    const int64_t group_size = RASTER_GM * tiles_n;
+    const int64_t group = tile / group_size, in_group = tile % group_size;
+    const int64_t first_m = group * RASTER_GM;
+    const int64_t gm = min((int64_t)RASTER_GM, tiles_m - first_m);
+    tm = first_m + in_group % gm;
+    tn = in_group / gm;
+}
+
 template <bool A_MN, bool B_MN, int CG, int CONV>
 __global__ void __launch_bounds__((4 * CG + 2) * 32, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
@@ -62,7 +75,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             bool ok = true;
             for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 const int64_t tile = item % num_tiles, split = item / num_tiles;
-                const int64_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                int64_t tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int64_t kb0 = split * p.kb_per_split;
                 const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
                 for (int64_t kb = kb0; kb < kb1; kb += KB_PER_STAGE, ++it) {
@@ -134,7 +148,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         bool ok = true;
         for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             const int64_t tile = item % num_tiles, split = item / num_tiles;
-            const int64_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            int64_t tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             const int64_t kb0 = split * p.kb_per_split;
             const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
             const int64_t rowblk = tm * (BM / QB) + quad;
