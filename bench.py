@@ -201,13 +201,13 @@ def run_ours(args):
 
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()     # after rank 0's sampler start-up, so that no rank's timed region contains another rank's set-up
     torch.cuda.synchronize()
     t_wall0 = time.time()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

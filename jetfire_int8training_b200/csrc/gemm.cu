@@ -62,16 +62,30 @@ struct GemmParams {
     int stochastic; const float* noise; uint64_t seed, offset;
 };
 
+#ifdef JF_TIMELINE
+// tuning builds only: clock stamps of CTA 0 (first events of the launch), read back with jf_debug_timeline
+__device__ long long g_timeline[8192];
+#define JF_STAMP(cond, idx) do { if ((cond) && blockIdx.x == 0) g_timeline[(idx)] = clock64(); } while (0)
+#define JF_TL_ON true
+#else
+#define JF_TL_ON false
+#define JF_STAMP(cond, idx) do { } while (0)
+#endif
 __device__ int g_gemm_error = 0;   // 0 = ok; otherwise the code of the first wait that expired
 
-template <bool BACKOFF = false>
+// Wait for a barrier phase, giving up after WAIT_BUDGET_CLOCKS.  SUSPEND = true (producer and issuer warps): every try lets the
+// hardware park the thread for up to 2 us, so the waiting warp issues next to nothing; SUSPEND = false (consumers): plain
+// try_wait polling.
+#ifndef JF_CONSUMER_SUSPEND
+#define JF_CONSUMER_SUSPEND 0
+#endif
+template <bool SUSPEND = (JF_CONSUMER_SUSPEND != 0)>
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
-        if (BACKOFF) __nanosleep(20);
-        if ((it & 255u) == 255u) {
+        if (SUSPEND ? ptx::mbar_try_wait_hint(bar, parity, 2000u) : ptx::mbar_try_wait(bar, parity)) return true;
+        if ((it & (SUSPEND ? 31u : 255u)) == (SUSPEND ? 31u : 255u)) {
             if (*abort_flag) return false;
             if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
                 *abort_flag = code;
@@ -92,7 +106,7 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
 // CONV_INT32 adds the raw integers (diagnostic int32 GEMM); the CONV_PROBE_* modes exist only to time the kernel's
 // data movement without its arithmetic and produce meaningless results.
 // ---------------------------------------------------------------------------------------------------------
-enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_MIXED = 3, CONV_INT32 = 4, CONV_PROBE_NONE = 5, CONV_PROBE_NOLD = 6 };
+enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_MIXED = 3, CONV_INT32 = 4, CONV_PROBE_NONE = 5 };
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
     uint64_t r;
@@ -111,25 +125,25 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     return r;
 }
 
-// acc2[j] (pairs) += s * float(r[2j], r[2j+1]) for the 32 int32 values in r
-template <int CONV>
-__device__ __forceinline__ void scale_accumulate(uint64_t (&acc2)[16], const uint32_t (&r)[32], float s) {
+// acc2[j] (NV/2 packed pairs) += s * float(r[2j], r[2j+1]) for the NV int32 values in r
+template <int CONV, int NV>
+__device__ __forceinline__ void scale_accumulate(uint64_t* acc2, const uint32_t* r, float s) {
     if (CONV == CONV_INT32) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NV / 2; ++j) {
             const uint32_t lo = (uint32_t)acc2[j] + r[2 * j], hi = (uint32_t)(acc2[j] >> 32) + r[2 * j + 1];
             acc2[j] = ((uint64_t)hi << 32) | lo;
         }
         return;
     }
-    if (CONV == CONV_PROBE_NONE || CONV == CONV_PROBE_NOLD) {
+    if (CONV == CONV_PROBE_NONE) {
         acc2[0] += ((uint64_t)r[1] << 32) | r[0];
         return;
     }
     const uint64_t s2 = pack2(s, s);
     const uint64_t negc = pack2(-12582912.0f, -12582912.0f);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < NV / 2; ++j) {
         const bool magic = (CONV == CONV_MAGIC) || (CONV == CONV_MIXED && (j & 1));
         if (magic) {
             const uint64_t x = add2(pack2(__int_as_float((int)r[2 * j] + 0x4B400000), __int_as_float((int)r[2 * j + 1] + 0x4B400000)), negc);
@@ -430,5 +444,11 @@ int jf_igemm_error_flag(void) {
     if (v != 0) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
     return v;
 }
+
+#ifdef JF_TIMELINE
+int jf_debug_timeline(long long* host_out, int n) {
+    return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(long long) * (size_t)n) == cudaSuccess ? 0 : JF_ERR_LAUNCH;
+}
+#endif
 
 }  // extern "C"

@@ -1,18 +1,31 @@
 // The persistent per-block INT8 GEMM kernel (included by gemm.cu inside namespace jf, after the helpers it uses).
 //
-// CG = column groups of the consumer side: 4*CG consumer warps, each thread owns one row and 128/CG columns.
+// Warp roles (11 warps): 8 consumer warps, 1 TMA producer warp, 2 MMA-issuing warps (one lane each).
 //
-// Accumulators are handed over in GROUPS of two K blocks: the issuer waits for a free group, issues the two MMAs of the pair
-// (one per 128-column accumulator) and signals the pair with ONE tcgen05.commit.  Measured on B200: with one commit per
-// 128x128x32 MMA, the MMA -> commit -> mbarrier hand-over -- not the tensor core, the TMEM reads or TMA -- set a floor of about
-// 600 SM clocks per K block (clock-stamped timeline: ~1600 clocks from the commit to the consumer seeing it with four
-// accumulators in flight; the floor stayed when TMEM loads, arithmetic and even the TMA loads were removed).
+// Hand-over of the accumulators.  Tensor memory holds two GROUPS of two 128-column accumulators.  The four K blocks of a
+// shared-memory stage form two pairs; pair 0 goes to group 0 and is issued by issuer 0, pair 1 to group 1 / issuer 1, each pair
+// is signalled with ONE tcgen05.commit.  Two issuers because the cost of issuing is the issuing thread's, not the tensor pipe's:
+// measured on B200 with a single-CTA microbenchmark, a thread that loops over [tcgen05.mma ; tcgen05.commit] needs ~457 SM clocks
+// per iteration whatever the MMA's N (16..256), ~110 more per additional MMA before the commit -- and two such threads in
+// different warps run at that rate EACH.  The shared-memory stage is released by a consumer warp once it has seen the stage's
+// last pair complete, which saves the issuers a third commit per stage.
+//
+// Consumers.  Warp w owns TMEM lanes 32*(w%4).. (rows) and columns 64*(w/4).. of every accumulator: a thread is one row of two
+// 32x32 quantisation blocks (64 fp32 accumulators in registers).  The arithmetic is bound by instruction issue -- per element
+// one int32 -> fp32 conversion and one FMA (fma.f32x2 occupies two issue cycles): >= 256 clocks per 128x128x32 K block per SM
+// against 64 clocks of tensor-core time -- so the loop is built to keep the issue slots busy: few fat warps (twice the
+// arithmetic per barrier / fence / tcgen05.ld round trip of a 16-warp layout; a clock-stamped timeline of the 16-warp version
+// showed ~800 clocks per K block per warp for ~110 issue cycles), and the 32-column TMEM load of the next half K block is always
+// in flight while the current half is converted and accumulated (two register buffers).
 #pragma once
 
 // Tile rasterisation: tiles are numbered in groups of RASTER_GM tile-rows, M-fastest inside a group, so the ~148 tiles that
 // are in flight together cover about 16 x 9 tiles: 16 A panels + 9 B panels (~26 MB at K = 8192) instead of a whole
 // 64-row-panel column of A, which did not stay in L2 (ncu: 1.12 GB of DRAM traffic per 8192^3 launch against 0.2 GB algorithmic).
 constexpr int RASTER_GM = 16;
+constexpr int EPI_WARPS = 16;                      // consumer warps
+constexpr int NUM_ISSUERS = 2;                     // MMA-issuing warps = accumulator groups
+constexpr int GEMM_THREADS = (EPI_WARPS + 1 + NUM_ISSUERS) * 32;
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
     const int64_t group_size = RASTER_GM * tiles_n;
     const int64_t group = tile / group_size, in_group = tile % group_size;
@@ -22,15 +35,13 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
     tn = in_group / gm;
 }
 
-template <bool A_MN, bool B_MN, int CG, int CONV>
-__global__ void __launch_bounds__((4 * CG + 2) * 32, 1)
+template <bool A_MN, bool B_MN, int CONV>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-    constexpr int EPI_WARPS = 4 * CG;
-    constexpr int WARP_TMA = EPI_WARPS, WARP_MMA = EPI_WARPS + 1;
-    constexpr int NBLK = 4 / CG;          // 32-column blocks per thread (2 or 1)
+    constexpr int WARP_TMA = EPI_WARPS, WARP_MMA = EPI_WARPS + 1;   // issuers: WARP_MMA, WARP_MMA + 1
     constexpr bool INT32ACC = (CONV == CONV_INT32);
-    constexpr int NUM_GRP = 2, GRP_COLS = 2 * BN;   // two groups of two 128-column accumulators = all 512 TMEM columns
-    static_assert(CG == 2 || CG == 4, "CG");
+    constexpr int NUM_GRP = NUM_ISSUERS, GRP_COLS = 2 * BN;   // two groups of two 128-column accumulators = all 512 TMEM columns
+    static_assert(NUM_GRP * GRP_COLS == TMEM_COLS && KB_PER_STAGE == 2 * NUM_GRP, "a stage = one pair of K blocks per group");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -38,7 +49,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint8_t* smem_b = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * STAGES * STAGE_BYTES);
     uint64_t* full_bar = bars;                            // [STAGES]   TMA -> MMA
-    uint64_t* empty_bar = bars + STAGES;                  // [STAGES]   MMA -> TMA
+    uint64_t* empty_bar = bars + STAGES;                  // [STAGES]   consumers (int32 mode: MMA) -> TMA
     uint64_t* grp_full = bars + 2 * STAGES;               // [NUM_GRP]  MMA -> consumers
     uint64_t* grp_empty = bars + 2 * STAGES + NUM_GRP;    // [NUM_GRP]  consumers -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NUM_GRP);
@@ -91,11 +102,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
         }
-    } else if (warp == WARP_MMA) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+    } else if (warp >= WARP_MMA) {
+        // ------------------------------------------------------------------ MMA issuers
+        const uint32_t w = (uint32_t)(warp - WARP_MMA);   // issuer index = accumulator group it owns
+        if (lane == 0 && !(INT32ACC && w != 0)) {
             constexpr uint32_t idesc = ptx::make_idesc_i8(BM, BN, A_MN, B_MN);
-            uint32_t it = 0, gi = 0;   // running stage / accumulator-group counters
+            uint32_t it = 0, gi = 0;   // running stage counter / uses of the accumulator group (int32 mode: tile counter)
             bool ok = true;
             for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 const int64_t split = item / num_tiles;
@@ -103,15 +115,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
                 for (int64_t kb = kb0; kb < kb1 && ok; kb += KB_PER_STAGE, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    const int nblk = (int)min((int64_t)KB_PER_STAGE, kb1 - kb);
+                    if (!INT32ACC && nblk <= 2 * (int)w) continue;   // the stage holds no K block of this issuer's pair
                     if (!(ok = bounded_wait<true>(&full_bar[s], ph, abort_flag, 2))) break;
                     ptx::tc_fence_after();
                     // descriptors of K block 0 of the stage; K block j is 32 bytes further along a K-major row and 32 K-rows
                     // (4096 B) further in an MN-major tile, i.e. +2 / +256 in the descriptor's 16-byte address units
                     const uint64_t da0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem_a + s * STAGE_BYTES), A_MN ? 128 * 128 : 16, 1024);
                     const uint64_t db0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem_b + s * STAGE_BYTES), B_MN ? 128 * 128 : 16, 1024);
-                    const int nblk = (int)min((int64_t)KB_PER_STAGE, kb1 - kb);
                     if (INT32ACC) {
-                        // diagnostic mode: the tensor core accumulates the whole K range in one accumulator of one group
+                        // diagnostic mode: one issuer; the tensor core accumulates the whole K range of a tile in one accumulator
                         const uint32_t g = gi % NUM_GRP;
                         for (int j = 0; j < nblk && ok; ++j) {
                             const bool first = (kb + j == kb0), last = (kb + j + 1 == kb1);
@@ -123,114 +136,122 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                          db0 + (uint64_t)(B_MN ? j * 256 : j * 2), idesc, first ? 0u : 1u);
                             if (last) { ptx::umma_commit(&grp_full[g]); ++gi; }
                         }
+                        if (ok) ptx::umma_commit(&empty_bar[s]);   // no consumer sees the stages of this mode: the issuer frees them
                     } else {
-                        for (int j0 = 0; j0 < nblk && ok; j0 += 2, ++gi) {
-                            const uint32_t g = gi % NUM_GRP;
-                            if (!(ok = bounded_wait<true>(&grp_empty[g], ((gi / NUM_GRP) & 1u) ^ 1u, abort_flag, 3))) break;
-                            ptx::tc_fence_after();
-                            const int npair = min(2, nblk - j0);
-                            for (int jj = 0; jj < npair; ++jj) {
-                                const int j = j0 + jj;
-                                ptx::umma_i8(tmem_base + g * GRP_COLS + jj * BN, da0 + (uint64_t)(A_MN ? j * 256 : j * 2),
-                                             db0 + (uint64_t)(B_MN ? j * 256 : j * 2), idesc, 0u);
-                            }
-                            ptx::umma_commit(&grp_full[g]);
+                        if (!(ok = bounded_wait<true>(&grp_empty[w], (gi & 1u) ^ 1u, abort_flag, 3))) break;
+                        ptx::tc_fence_after();
+                        const int npair = min(2, nblk - 2 * (int)w);
+                        for (int jj = 0; jj < npair; ++jj) {
+                            const int j = 2 * (int)w + jj;
+                            ptx::umma_i8(tmem_base + w * GRP_COLS + jj * BN, da0 + (uint64_t)(A_MN ? j * 256 : j * 2),
+                                         db0 + (uint64_t)(B_MN ? j * 256 : j * 2), idesc, 0u);
                         }
+                        ptx::umma_commit(&grp_full[w]);
+                        ++gi;
                     }
-                    if (ok) ptx::umma_commit(&empty_bar[s]);
                 }
             }
         }
     } else {
         // ------------------------------------------------------------------ consumers
-        const int quad = warp & 3, cgrp = warp >> 2;
-        uint32_t gi = 0;
+        const int quad = warp & 3, cgrp = warp >> 2;   // TMEM lane quadrant (rows) / 32-column group of every accumulator
+        uint32_t use0 = 0, use1 = 0, sit = 0;   // uses of group 0 / 1 (int32 mode: use0 counts tiles) / running stage counter
         bool ok = true;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + cgrp * 32;
         for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const int64_t tile = item % num_tiles, split = item / num_tiles;
-            int64_t tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-            const int64_t kb0 = split * p.kb_per_split;
-            const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
-            const int64_t rowblk = tm * (BM / QB) + quad;
-            const int64_t colblk0 = tn * (BN / QB) + cgrp * NBLK;
-            const bool row_ok = rowblk < p.M / QB;
-            const bool col_ok0 = colblk0 < p.N / QB, col_ok1 = (NBLK > 1) && (colblk0 + 1 < p.N / QB);
+            int tm32, tn32, split32;
+            {
+                const int64_t tile = item % num_tiles;
+                int64_t tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                tm32 = (int)tm; tn32 = (int)tn; split32 = (int)(item / num_tiles);
+            }
+            const int kb0 = (int)(split32 * p.kb_per_split);
+            const int kb1 = (int)min(p.nkb, (int64_t)kb0 + p.kb_per_split);
+            const int rowblk = tm32 * (BM / QB) + quad;
+            const int colblk = tn32 * (BN / QB) + cgrp;
+            const bool blk_ok = rowblk < (int)(p.M / QB) && colblk < (int)(p.N / QB);   // warp-uniform
 
-            uint64_t acc2[NBLK][16];   // fp32 accumulators as packed pairs, one 32-column block per row of the array
+            uint64_t acc2[16];   // 32 fp32 accumulators as packed pairs
 #pragma unroll
-            for (int b = 0; b < NBLK; ++b)
-#pragma unroll
-                for (int j = 0; j < 16; ++j) acc2[b][j] = 0ull;
+            for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
 
-            // lane-distributed scale fetch: lanes 0-7 hold sa for 8 consecutive K blocks, 8-15 sb of column block 0, 16-23 of block 1
-            auto fetch_scales = [&](int64_t p0) -> float {
-                const int which = lane >> 3;
-                const int64_t pp = p0 + (lane & 7);
-                float v = 0.f;
-                if (pp < kb1) {
-                    if (which == 0) { if (row_ok) v = __half2float(__ldg(p.sa + rowblk * p.sa_sm + pp * p.sa_sk)); }
-                    else if (which == 1) { if (col_ok0) v = __half2float(__ldg(p.sb + colblk0 * p.sb_sn + pp * p.sb_sk)); }
-                    else if (which == 2) { if (col_ok1) v = __half2float(__ldg(p.sb + (colblk0 + 1) * p.sb_sn + pp * p.sb_sk)); }
+            // lanes 0-7 hold the scale products sa*sb of 8 consecutive K blocks
+            const __half* sa_ptr = p.sa + (int64_t)rowblk * p.sa_sm + (int64_t)(kb0 + (lane & 7)) * p.sa_sk;
+            const __half* sb_ptr = p.sb + (int64_t)colblk * p.sb_sn + (int64_t)(kb0 + (lane & 7)) * p.sb_sk;
+            // The two loads are volatile asm so that they are ISSUED here, eight K blocks before their values are needed (a plain
+            // __ldg is sunk by the compiler to its first use, which exposed the load latency once per eight K blocks).
+            auto fetch_scales = [&](int t8) -> float {   // t8 = first K block (relative to kb0) of the group of 8
+                unsigned short ha = 0, hb = 0;
+                if (lane < 8 && kb0 + t8 + (lane & 7) < kb1 && blk_ok) {
+                    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(ha) : "l"(sa_ptr + (int64_t)t8 * p.sa_sk));
+                    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(hb) : "l"(sb_ptr + (int64_t)t8 * p.sb_sk));
                 }
-                return v;
+                return __fmul_rn(__half2float(__ushort_as_half(ha)), __half2float(__ushort_as_half(hb)));
             };
-            float sc_next = INT32ACC ? 0.f : fetch_scales(kb0);
+            float sc_next = INT32ACC ? 0.f : fetch_scales(0);
             float sc_cur = 0.f;
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + cgrp * (32 * NBLK);
-            const int64_t nloop = INT32ACC ? 1 : (kb1 - kb0);   // the int32 mode reads one accumulated tile
+            const int nloop = INT32ACC ? (kb1 > kb0 ? 1 : 0) : (kb1 - kb0);   // the int32 mode reads one accumulated tile
+            const uint32_t g32 = use0 % NUM_GRP;                               // int32 mode: the tile's group
 
-            // one accumulator (K block) of the current group: TMEM -> registers -> scale FMA
-            auto consume = [&](uint32_t taddr, int64_t t, bool release_after, uint32_t g) {
+            for (int t = 0; t < nloop; t += 2) {
+                // pair t/2 of the tile lives in group (t/2)%2
+                const uint32_t g = INT32ACC ? g32 : (uint32_t)((t >> 1) & 1);
+                const uint32_t acc = lane_base + g * GRP_COLS;
+                const bool tl = JF_TL_ON && blockIdx.x == 0 && threadIdx.x == 0 && item == blockIdx.x && t < 200;
+                JF_STAMP(tl, t * 8 + 0);
+                {
+                    const uint32_t uses = INT32ACC ? use0 / NUM_GRP : (g ? use1 : use0);
+                    const bool got = bounded_wait(&grp_full[g], uses & 1u, abort_flag, 4);
+                    if (!(ok = __all_sync(0xffffffffu, got))) break;   // warp-uniform exit
+                    if (g && !INT32ACC) ++use1; else ++use0;
+                    ptx::tc_fence_after();
+                }
+                JF_STAMP(tl, t * 8 + 1);
+                const bool two = (t + 1 < nloop);
                 const int pi = (int)(t & 7);
                 if (!INT32ACC && pi == 0) {
                     sc_cur = sc_next;
-                    sc_next = fetch_scales(kb0 + t + 8);
+                    sc_next = fetch_scales(t + 8);
                 }
-                const float sa_v = __shfl_sync(0xffffffffu, sc_cur, pi);
-                const float s0 = __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 8 + pi));
-                const float s1 = (NBLK > 1) ? __fmul_rn(sa_v, __shfl_sync(0xffffffffu, sc_cur, 16 + pi)) : 0.f;
-                uint32_t r0[32], r1[32];
-                if (CONV == CONV_PROBE_NOLD) {   // timing probe: no TMEM read at all
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) { r0[j] = (uint32_t)t; r1[j] = (uint32_t)t; }
-                } else {
-                    ptx::tmem_ld_32x32b_x32(taddr, r0);
-                    if (NBLK > 1) ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-                    ptx::tmem_wait_ld_regs(r0);
-                    if (NBLK > 1) ptx::tmem_wait_ld_regs(r1);
+                const float s0 = __shfl_sync(0xffffffffu, sc_cur, pi);
+                const float s1 = __shfl_sync(0xffffffffu, sc_cur, pi + 1);
+                // Registers (96 per thread with 19 warps) hold 32 accumulators + ONE accumulator's 32 raw columns: the pair's first
+                // K block is converted and accumulated before the second one is read, and only then can the group be released.
+                // Reading both first and releasing at once would shorten the hand-over (measured without arithmetic: 1.26 ms
+                // instead of 1.43 ms at 8192^3) but needs 64 raw registers, and the spills cost far more than that.
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(acc, r);
+                ptx::tmem_wait_ld_regs(r);
+                JF_STAMP(tl, t * 8 + 2);
+                if (two) {
+                    scale_accumulate<CONV, 32>(acc2, r, s0);
+                    JF_STAMP(tl, t * 8 + 3);
+                    ptx::tmem_ld_32x32b_x32(acc + BN, r);
+                    ptx::tmem_wait_ld_regs(r);
                 }
-                if (release_after) {
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&grp_empty[g]);
+                // the group's accumulators have left tensor memory: hand the group back to its issuer
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&grp_empty[g]);
+                if (!INT32ACC && (g == 1 || t + 2 >= nloop)) {
+                    // the last pair of a shared-memory stage has completed (the earlier pair was seen before): hand the stage
+                    // back to the TMA producer
+                    if (warp == 0 && lane == 0) ptx::mbar_arrive(&empty_bar[sit % STAGES]);
+                    ++sit;
                 }
-                scale_accumulate<CONV>(acc2[0], r0, s0);
-                if (NBLK > 1) scale_accumulate<CONV>(acc2[NBLK - 1], r1, s1);
-            };
-
-            for (int64_t t = 0; t < nloop; t += 2, ++gi) {
-                const uint32_t g = gi % NUM_GRP;
-                if (!(ok = bounded_wait(&grp_full[g], (gi / NUM_GRP) & 1u, abort_flag, 4))) break;
-                ptx::tc_fence_after();
-                const bool two = (t + 1 < nloop);
-                consume(lane_base + g * GRP_COLS, t, !two, g);
-                if (two) consume(lane_base + g * GRP_COLS + BN, t + 1, true, g);
+                JF_STAMP(tl, t * 8 + 4);
+                scale_accumulate<CONV, 32>(acc2, r, two ? s1 : s0);
+                JF_STAMP(tl, t * 8 + 5);
             }
             if (!ok) break;
 
             // ---------------------------------------------------------------- tile epilogue
-            const int64_t row = tm * BM + quad * 32 + lane;
-            if (!row_ok) continue;
+            if (!blk_ok) continue;
+            float ab[32];
 #pragma unroll
-            for (int b = 0; b < NBLK; ++b) {
-                const bool col_ok = b == 0 ? col_ok0 : col_ok1;
-                if (!col_ok) continue;   // warp-uniform
-                float ab[32];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) unpack2(acc2[b][j], ab[2 * j], ab[2 * j + 1]);
-                store_block(p, ab, row, (colblk0 + b) * QB, rowblk, colblk0 + b, split, lane);
-            }
+            for (int j = 0; j < 16; ++j) unpack2(acc2[j], ab[2 * j], ab[2 * j + 1]);
+            store_block(p, ab, (int64_t)tm32 * BM + quad * 32 + lane, (int64_t)colblk * QB, rowblk, colblk, split32, lane);
         }
     }
 
@@ -238,6 +259,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == WARP_MMA) {
+        __syncwarp();
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
