@@ -1,6 +1,6 @@
 // The persistent per-block INT8 GEMM kernel (included by gemm.cu inside namespace jf, after the helpers it uses).
 //
-// Warp roles (11 warps): 8 consumer warps, 1 TMA producer warp, 2 MMA-issuing warps (one lane each).
+// Warp roles (19 warps): 16 consumer warps, 1 TMA producer warp, 2 MMA-issuing warps (one lane each).
 //
 // Hand-over of the accumulators.  Tensor memory holds two GROUPS of two 128-column accumulators.  The four K blocks of a
 // shared-memory stage form two pairs; pair 0 goes to group 0 and is issued by issuer 0, pair 1 to group 1 / issuer 1, each pair
@@ -10,13 +10,15 @@
 // different warps run at that rate EACH.  The shared-memory stage is released by a consumer warp once it has seen the stage's
 // last pair complete, which saves the issuers a third commit per stage.
 //
-// Consumers.  Warp w owns TMEM lanes 32*(w%4).. (rows) and columns 64*(w/4).. of every accumulator: a thread is one row of two
-// 32x32 quantisation blocks (64 fp32 accumulators in registers).  The arithmetic is bound by instruction issue -- per element
-// one int32 -> fp32 conversion and one FMA (fma.f32x2 occupies two issue cycles): >= 256 clocks per 128x128x32 K block per SM
-// against 64 clocks of tensor-core time -- so the loop is built to keep the issue slots busy: few fat warps (twice the
-// arithmetic per barrier / fence / tcgen05.ld round trip of a 16-warp layout; a clock-stamped timeline of the 16-warp version
-// showed ~800 clocks per K block per warp for ~110 issue cycles), and the 32-column TMEM load of the next half K block is always
-// in flight while the current half is converted and accumulated (two register buffers).
+// Consumers.  Warp w owns TMEM lanes 32*(w%4).. (rows) and columns 32*(w/4).. of every accumulator: a thread is one row of one
+// 32x32 quantisation block (32 fp32 accumulators in registers).  Every consumer warp has to walk through every K block, so the
+// length of one warp's chain per pair (barrier test, fences, two tcgen05.ld round trips, release, 2 x 48 arithmetic
+// instructions under four-way issue contention) is what bounds the kernel, not the tensor core (64 clocks per K block), the
+// issuers or the operand stream: with the arithmetic removed the same kernel runs 8192^3 in 1.13 ms, with it in 2.07 ms.
+// Measured alternatives that were slower: 8 consumer warps x 64 columns (2.73 ms), four single-accumulator slots with one
+// commit per K block (2.92 ms), 16-column chunks with the next chunk's load in flight (2.20 ms), reading both accumulators of a
+// pair before the arithmetic so the group is released at once (1.26 ms without arithmetic, but 64 raw registers spill at the 96
+// registers per thread that 19 warps allow: 3.6 - 6 ms).
 #pragma once
 
 // Tile rasterisation: tiles are numbered in groups of RASTER_GM tile-rows, M-fastest inside a group, so the ~148 tiles that
@@ -198,7 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 // pair t/2 of the tile lives in group (t/2)%2
                 const uint32_t g = INT32ACC ? g32 : (uint32_t)((t >> 1) & 1);
                 const uint32_t acc = lane_base + g * GRP_COLS;
-                const bool tl = JF_TL_ON && blockIdx.x == 0 && threadIdx.x == 0 && item == blockIdx.x && t < 200;
+                [[maybe_unused]] const bool tl = JF_TL_ON && blockIdx.x == 0 && threadIdx.x == 0 && item == blockIdx.x && t < 200;
                 JF_STAMP(tl, t * 8 + 0);
                 {
                     const uint32_t uses = INT32ACC ? use0 / NUM_GRP : (g ? use1 : use0);
