@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the Jetfire INT8 hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload linear|nonlinear]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload linear|nonlinear|gpt2|gemm_sweep]
 
 Default workload ("linear"): one per-block (32x32) INT8 linear layer at the headline GEMM shape M = N = K = 8192 --
 forward Y = X W^T, input gradient dX = dY W (stochastic rounding) and weight gradient dW = dY^T X -- i.e. three GEMM
@@ -534,13 +534,61 @@ def run_gpt2(args):
         dist.destroy_process_group()
 
 
+def run_gemm_sweep(args):
+    """Secondary workload: forward / dgrad / wgrad GEMM TOPS over the square sizes and the GPT-2 layer shapes (M = 8192 tokens),
+    through the Python operator API on device-resident operands; torch._int_mm (plain int32 GEMM, no block scaling) beside it."""
+    import torch
+    from jetfire_int8training_b200 import Linear, rng
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rng.manual_seed(7)
+    g = torch.Generator(device=dev).manual_seed(0)
+    shapes = [(n, n, n) for n in (1024, 2048, 4096, 8192, 16384)] + [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768),
+                                                                     (8192, 768, 3072)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        tot = 0.0
+        for _ in range(n):
+            flush.zero_()                       # operands of the small shapes would otherwise sit in the 126 MB L2
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            tot += a.elapsed_time(b)
+        return tot / n
+
+    out = {}
+    for M, N, K in shapes:      # tokens M, out features N, in features K
+        X8 = torch.randint(-127, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+        W8 = torch.randint(-127, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+        G8 = torch.randint(-127, 128, (M, N), generator=g, device=dev, dtype=torch.int8)
+        sc = lambda r, c: (torch.rand(r, c, generator=g, device=dev) * 0.099 + 1e-3).half()
+        SX, SW, SG = sc(M // 32, K // 32), sc(N // 32, K // 32), sc(M // 32, N // 32)
+        n = 3 if M * N * K > 2 ** 40 else 10
+        ops = 2.0 * M * N * K
+        t_f = timed(lambda: Linear.int8_linear_forward(X8, SX, W8, SW, True, 32), n)
+        t_b = timed(lambda: Linear.int8_linear_backward(X8, SX, G8, SG, None, W8, SW, 32, stochastic=True), n)
+        t_w = timed(lambda: Linear.int8_linear_wgrad(X8, SX, G8, SG), n)
+        t_d = max(t_b - t_w, 1e-6)
+        t_c = timed(lambda: torch._int_mm(X8, W8.t()), n) if M > 32 else float("nan")
+        out[f"{M}x{N}x{K}"] = {"fwd_ms": round(t_f, 4), "fwd_tops": round(ops / t_f / 1e9, 1), "dgrad_sr_ms": round(t_d, 4),
+                               "dgrad_sr_tops": round(ops / t_d / 1e9, 1), "wgrad_ms": round(t_w, 4),
+                               "wgrad_tops": round(ops / t_w / 1e9, 1), "int_mm_tops": round(ops / t_c / 1e9, 1)}
+        del X8, W8, G8
+    print(json.dumps({"metric": "per-block INT8 GEMM TOPS", "unit": "TOPS", "shape": "tokens x out_features x in_features",
+                      "note": "CUDA events per call, 256 MB L2 flush before every call; dgrad = (dgrad + wgrad) - wgrad",
+                      "shapes": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear", "gpt2"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear", "gpt2", "gemm_sweep"])
     ap.add_argument("--model", default="124M", choices=["124M", "xl", "tiny"], help="gpt2 workload: model size")
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the linear workload")
@@ -557,6 +605,8 @@ def main():
         run_nonlinear(args)
     elif args.workload == "gpt2":
         run_gpt2(args)
+    elif args.workload == "gemm_sweep":
+        run_gemm_sweep(args)
     else:
         run_ours(args)
 

@@ -441,6 +441,39 @@ __device__ __forceinline__ float gelu_cdf(float x, float* ex) {
     return x < 0.f ? half_erfc : __fsub_rn(1.0f, half_erfc);
 }
 
+// Both GELU kernels go through a per-block lookup table: inside one 32x32 quantisation block the input is q * s with a single
+// scale s, so it takes at most 256 different values, and so does any function of it.  Per tile the warp evaluates the function
+// once for every payload value of each of its blocks (256 * TW/32 evaluations instead of 32 * TW) into shared memory, and every
+// element costs one shift + mask + shared-memory load.  The result is bit-identical to evaluating the function per element.
+template <int TW, class F>
+__device__ __forceinline__ void build_block_lut(float* lut /* [TW/32][256] of this warp */, float my_scale, const Tile& t, F&& f) {
+    constexpr int BLOCKS = TW / 32, PER_LANE = BLOCKS * 256 / 32;
+    __syncwarp();   // the previous tile's lookups are done
+    const int e0 = t.lane * PER_LANE;            // entries e0 .. e0 + PER_LANE - 1, all inside one block's table
+    const int b = e0 >> 8;
+    // the scale of block b is held by the lanes whose chunk lies in that block: take it from row group 0, chunk 2b
+    const float sc = __shfl_sync(0xffffffffu, my_scale, 2 * b);
+    float out[PER_LANE];
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) out[j] = f((float)(int8_t)(uint8_t)((e0 + j) & 255), sc);
+#pragma unroll
+    for (int j = 0; j < PER_LANE; j += 4)
+        *reinterpret_cast<float4*>(lut + e0 + j) = make_float4(out[j], out[j + 1], out[j + 2], out[j + 3]);
+    __syncwarp();
+}
+// the 16 table values of one row chunk (payload bytes in r) from this lane's block table
+__device__ __forceinline__ void lookup16(const float* lut_b, const int4& r, float (&f)[16]) {
+    const uint32_t w[4] = {(uint32_t)r.x, (uint32_t)r.y, (uint32_t)r.z, (uint32_t)r.w};
+    const char* base = reinterpret_cast<const char*>(lut_b);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t off = (j == 0) ? ((w[k] << 2) & 0x3FCu) : ((w[k] >> (8 * j - 2)) & 0x3FCu);
+            f[4 * k + j] = *reinterpret_cast<const float*>(base + off);
+        }
+}
+
 // forward: x = fp16(q*s); y = x * Phi(x); block quantise with amax + 5e-5
 template <int TW>
 __global__ void __launch_bounds__(THREADS, TW == 64 ? 2 : 1)
@@ -448,6 +481,8 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
                 __half* __restrict__ sy) {
     constexpr int NP = Geo<TW>::NP;
     using Raw = RawQ<NP>;
+    __shared__ __align__(16) float lut_all[WARPS][TW / 32][256];
+    float* lut = &lut_all[threadIdx.x >> 5][0][0];
     for_each_tile<TW, Raw, true>(
         M, N,
         [&](const Tile& t, Raw& r) {
@@ -455,18 +490,15 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
             r.sc = load_scale16(sx, t, N);
         },
         [&](const Tile& t, Raw& r) {
-            const __half2 s2 = __half2half2(r.sc);
+            build_block_lut<TW>(lut, __half2float(r.sc), t, [](float q, float sc) {
+                const float x = __half2float(__hmul_rn(__float2half_rn(q), __float2half_rn(sc)));   // the reference's fp16 product
+                float e;
+                return __fmul_rn(gelu_cdf(x, &e), x);
+            });
+            const float* lut_b = lut + (t.cc >> 1) * 256;
             float v[NP][16];
 #pragma unroll
-            for (int i = 0; i < NP; ++i) {
-                float f[16];
-                dequant16_h(r.d[i], s2, f);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float e;
-                    v[i][j] = __fmul_rn(gelu_cdf(f[j], &e), f[j]);
-                }
-            }
+            for (int i = 0; i < NP; ++i) lookup16(lut_b, r.d[i], v[i]);
             const float amax = __fadd_rn(block_max<TW>(absmax_tile<NP>(v)), 5e-5f);
             const float scale32 = __fdiv_rn(amax, 127.0f);
             SrCfg sr{nullptr, 0, 0};
@@ -484,6 +516,8 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
                 const __half* __restrict__ sg, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd, SrCfg sr) {
     constexpr int NP = Geo<TW>::NP;
     using Raw = RawQ2<NP>;
+    __shared__ __align__(16) float lut_all[WARPS][TW / 32][256];
+    float* lut = &lut_all[threadIdx.x >> 5][0][0];
     for_each_tile<TW, Raw, true>(
         M, N,
         [&](const Tile& t, Raw& r) {
@@ -493,22 +527,23 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
             r.sb = load_scale16(sg, t, N);
         },
         [&](const Tile& t, Raw& r) {
-            const float scx = __half2float(r.sa), scg = __half2float(r.sb);
+            build_block_lut<TW>(lut, __half2float(r.sa), t, [](float q, float sc) {
+                const float x = __fmul_rn(q, sc);
+                float e;
+                const float cdf = gelu_cdf(x, &e);
+                const float pdf = __fmul_rn(__fmul_rn(x, 0.3989422804014327f), e);
+                return __fadd_rn(cdf, pdf);
+            });
+            const float* lut_b = lut + (t.cc >> 1) * 256;
+            const float scg = __half2float(r.sb);
             float v[NP][16];
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
-                float fx[16], fg[16];
-                unpack16(r.a[i], fx);
+                float fd[16], fg[16];
+                lookup16(lut_b, r.a[i], fd);
                 unpack16(r.b[i], fg);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float x = __fmul_rn(fx[j], scx);
-                    const float g = __fmul_rn(fg[j], scg);
-                    float e;
-                    const float cdf = gelu_cdf(x, &e);
-                    const float pdf = __fmul_rn(__fmul_rn(x, 0.3989422804014327f), e);
-                    v[i][j] = __fmul_rn(__fadd_rn(cdf, pdf), g);
-                }
+                for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(fd[j], __fmul_rn(fg[j], scg));
             }
             const float scale32 = __fdiv_rn(block_max<TW>(absmax_tile<NP>(v)), 127.0f);
             emit_quantized<TW, false, SR, false>([&](int i, float (&a)[16]) {
