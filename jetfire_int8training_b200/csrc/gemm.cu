@@ -81,6 +81,9 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
+#ifdef JF_TIMELINE
+        if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_timeline[8000 + code]), 1ull);   // polls per wait site
+#endif
         if (SUSPEND ? ptx::mbar_try_wait_hint(bar, parity, 2000u) : ptx::mbar_try_wait(bar, parity)) return true;
         if ((it & (SUSPEND ? 31u : 255u)) == (SUSPEND ? 31u : 255u)) {
             if (*abort_flag) return false;
@@ -100,10 +103,11 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
 //   CONV_MAGIC: bits(I + 0x4B400000) is the float 1.5*2^23 + I; subtracting 1.5*2^23 (exact) leaves float(I)
 //               (integer pipe + FMA pipe)
 //   CONV_MIXED: alternate pairs between the two, to spread the work over three pipes.
+//   CONV_SCALAR: cvt.rn.f32.s32 + scalar fma.rn.f32 (no packed pairs)
 // CONV_INT32 adds the raw integers (diagnostic int32 GEMM); the CONV_PROBE_* modes exist only to time the kernel's
 // data movement without its arithmetic and produce meaningless results.
 // ---------------------------------------------------------------------------------------------------------
-enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_MIXED = 3, CONV_INT32 = 4, CONV_PROBE_NONE = 5 };
+enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_SCALAR = 2, CONV_MIXED = 3, CONV_INT32 = 4, CONV_PROBE_NONE = 5 };
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
     uint64_t r;
@@ -120,6 +124,37 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
+}
+
+// The 32 fp32 accumulators of a consumer thread: packed pairs for the fma.rn.f32x2 forms, plain floats for CONV_SCALAR.
+template <int CONV>
+struct Accum {
+    uint64_t v[16];
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0ull;
+    }
+    __device__ __forceinline__ void get(float (&ab)[32]) const {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) unpack2(v[j], ab[2 * j], ab[2 * j + 1]);
+    }
+};
+template <>
+struct Accum<CONV_SCALAR> {
+    float v[32];
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    }
+    __device__ __forceinline__ void get(float (&ab)[32]) const {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ab[j] = v[j];
+    }
+};
+// CONV_SCALAR: acc[j] = fma(s, float(r[j]), acc[j]) with scalar instructions (no register pairing needed)
+__device__ __forceinline__ void scale_accumulate_scalar(float* acc, const uint32_t* r, float s) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[j] = __fmaf_rn(s, __int2float_rn((int)r[j]), acc[j]);
 }
 
 // acc2[j] (NV/2 packed pairs) += s * float(r[2j], r[2j+1]) for the NV int32 values in r

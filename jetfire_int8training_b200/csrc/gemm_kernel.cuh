@@ -174,9 +174,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int colblk = tn32 * (BN / QB) + cgrp;
             const bool blk_ok = rowblk < (int)(p.M / QB) && colblk < (int)(p.N / QB);   // warp-uniform
 
-            uint64_t acc2[16];   // 32 fp32 accumulators as packed pairs
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
+            Accum<CONV> acc_regs;   // the thread's 32 fp32 accumulators
+            acc_regs.clear();
+            auto accumulate = [&](const uint32_t (&raw)[32], float sc) {
+                if constexpr (CONV == CONV_SCALAR) scale_accumulate_scalar(acc_regs.v, raw, sc);
+                else scale_accumulate<CONV, 32>(acc_regs.v, raw, sc);
+            };
 
             // lanes 0-7 hold the scale products sa*sb of 8 consecutive K blocks
             const __half* sa_ptr = p.sa + (int64_t)rowblk * p.sa_sm + (int64_t)(kb0 + (lane & 7)) * p.sa_sk;
@@ -227,7 +230,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 ptx::tmem_wait_ld_regs(r);
                 JF_STAMP(tl, t * 8 + 2);
                 if (two) {
-                    scale_accumulate<CONV, 32>(acc2, r, s0);
+                    accumulate(r, s0);
                     JF_STAMP(tl, t * 8 + 3);
                     ptx::tmem_ld_32x32b_x32(acc + BN, r);
                     ptx::tmem_wait_ld_regs(r);
@@ -243,7 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     ++sit;
                 }
                 JF_STAMP(tl, t * 8 + 4);
-                scale_accumulate<CONV, 32>(acc2, r, two ? s1 : s0);
+                accumulate(r, two ? s1 : s0);
                 JF_STAMP(tl, t * 8 + 5);
             }
             if (!ok) break;
@@ -251,8 +254,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             // ---------------------------------------------------------------- tile epilogue
             if (!blk_ok) continue;
             float ab[32];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) unpack2(acc2[j], ab[2 * j], ab[2 * j + 1]);
+            acc_regs.get(ab);
             store_block(p, ab, (int64_t)tm32 * BM + quad * 32 + lane, (int64_t)colblk * QB, rowblk, colblk, split32, lane);
         }
     }
