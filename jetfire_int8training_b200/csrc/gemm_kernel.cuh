@@ -199,32 +199,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int nloop = INT32ACC ? (kb1 > kb0 ? 1 : 0) : (kb1 - kb0);   // the int32 mode reads one accumulated tile
             const uint32_t g32 = use0 % NUM_GRP;                               // int32 mode: the tile's group
 
-            for (int t = 0; t < nloop; t += 2) {
-                // pair t/2 of the tile lives in group (t/2)%2
-                const uint32_t g = INT32ACC ? g32 : (uint32_t)((t >> 1) & 1);
+            // One pair of K blocks (group g; `two` = the pair has its second K block; `stage_end` = last pair of its shared-memory
+            // stage).  Returns false when a wait expired.
+            // Registers (96 per thread with 19 warps) hold 32 accumulators + ONE accumulator's 32 raw columns: the pair's first
+            // K block is converted and accumulated before the second one is read, and only then can the group be released.
+            // Reading both first and releasing at once would shorten the hand-over (measured without arithmetic: 1.26 ms
+            // instead of 1.43 ms at 8192^3) but needs 64 raw registers, and the spills cost far more than that.
+            auto do_pair = [&](const uint32_t g, const bool two, const float s0, const float s1, const bool stage_end,
+                               [[maybe_unused]] const int t) -> bool {
                 const uint32_t acc = lane_base + g * GRP_COLS;
                 [[maybe_unused]] const bool tl = JF_TL_ON && blockIdx.x == 0 && threadIdx.x == 0 && item == blockIdx.x && t < 200;
                 JF_STAMP(tl, t * 8 + 0);
                 {
                     const uint32_t uses = INT32ACC ? use0 / NUM_GRP : (g ? use1 : use0);
                     const bool got = bounded_wait(&grp_full[g], uses & 1u, abort_flag, 4);
-                    if (!(ok = __all_sync(0xffffffffu, got))) break;   // warp-uniform exit
+                    if (!__all_sync(0xffffffffu, got)) return false;   // warp-uniform exit
                     if (g && !INT32ACC) ++use1; else ++use0;
                     ptx::tc_fence_after();
                 }
                 JF_STAMP(tl, t * 8 + 1);
-                const bool two = (t + 1 < nloop);
-                const int pi = (int)(t & 7);
-                if (!INT32ACC && pi == 0) {
-                    sc_cur = sc_next;
-                    sc_next = fetch_scales(t + 8);
-                }
-                const float s0 = __shfl_sync(0xffffffffu, sc_cur, pi);
-                const float s1 = __shfl_sync(0xffffffffu, sc_cur, pi + 1);
-                // Registers (96 per thread with 19 warps) hold 32 accumulators + ONE accumulator's 32 raw columns: the pair's first
-                // K block is converted and accumulated before the second one is read, and only then can the group be released.
-                // Reading both first and releasing at once would shorten the hand-over (measured without arithmetic: 1.26 ms
-                // instead of 1.43 ms at 8192^3) but needs 64 raw registers, and the spills cost far more than that.
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(acc, r);
                 ptx::tmem_wait_ld_regs(r);
@@ -239,7 +232,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&grp_empty[g]);
-                if (!INT32ACC && (g == 1 || t + 2 >= nloop)) {
+                if (!INT32ACC && stage_end) {
                     // the last pair of a shared-memory stage has completed (the earlier pair was seen before): hand the stage
                     // back to the TMA producer
                     if (warp == 0 && lane == 0) ptx::mbar_arrive(&empty_bar[sit % STAGES]);
@@ -248,6 +241,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 JF_STAMP(tl, t * 8 + 4);
                 accumulate(r, two ? s1 : s0);
                 JF_STAMP(tl, t * 8 + 5);
+                return true;
+            };
+
+            int t = 0;
+            if (!INT32ACC) {
+                // fast path: eight K blocks (two stages, groups 0 1 0 1) per iteration with everything about the pair a constant
+                for (; t + 8 <= nloop && ok; t += 8) {
+                    sc_cur = sc_next;
+                    sc_next = fetch_scales(t + 8);
+#pragma unroll
+                    for (int pp = 0; pp < 4; ++pp) {
+                        if (!ok) break;
+                        ok = do_pair((uint32_t)(pp & 1), true, __shfl_sync(0xffffffffu, sc_cur, 2 * pp),
+                                     __shfl_sync(0xffffffffu, sc_cur, 2 * pp + 1), (pp & 1) == 1, t + 2 * pp);
+                    }
+                }
+            }
+            for (; t < nloop && ok; t += 2) {
+                // remaining pairs: pair t/2 of the tile lives in group (t/2)%2 (the int32 mode: one accumulator per tile)
+                const uint32_t g = INT32ACC ? g32 : (uint32_t)((t >> 1) & 1);
+                const int pi = (int)(t & 7);
+                if (!INT32ACC && pi == 0) {
+                    sc_cur = sc_next;
+                    sc_next = fetch_scales(t + 8);
+                }
+                const float s0 = __shfl_sync(0xffffffffu, sc_cur, pi);
+                const float s1 = __shfl_sync(0xffffffffu, sc_cur, pi + 1);
+                ok = do_pair(g, t + 1 < nloop, s0, s1, g == 1 || t + 2 >= nloop, t);
             }
             if (!ok) break;
 
