@@ -59,7 +59,7 @@ struct GemmParams {
     const __half* sb; int64_t sb_sn, sb_sk;   // sb(j,p) = sb[j*sb_sn + p*sb_sk]
     int mode;
     int8_t* out8; __half* out_scale; __half* out16; float* out32; int32_t* out_i32;
-    int stochastic; const float* noise; uint64_t seed, offset;
+    int stochastic; const float* noise; uint64_t offset; PhiloxKeys keys;
 };
 
 #ifdef JF_TIMELINE
@@ -225,7 +225,7 @@ __device__ __forceinline__ void store_block(const GemmParams& p, const float (&a
                     const float4 n1 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8 + 4));
                     nz[0] = n0.x; nz[1] = n0.y; nz[2] = n0.z; nz[3] = n0.w; nz[4] = n1.x; nz[5] = n1.y; nz[6] = n1.z; nz[7] = n1.w;
                 } else {
-                    philox_noise8((uint64_t)(row * p.N + col + 8 * k8), p.seed, p.offset, nz);
+                    philox_noise8((uint64_t)(row * p.N + col + 8 * k8), p.keys, p.offset, nz);
                 }
             }
 #pragma unroll
@@ -403,7 +403,7 @@ int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_
     p.M = M; p.N = N; p.K = K; p.splits = 1; p.kb_per_split = K / QB;
     p.sa = (const __half*)sg; p.sa_sm = sg_stride_m; p.sa_sk = sg_stride_k;
     p.sb = (const __half*)sw; p.sb_sn = sw_stride_n; p.sb_sk = sw_stride_k;
-    p.stochastic = stochastic; p.noise = noise; p.seed = seed; p.offset = offset;
+    p.stochastic = stochastic; p.noise = noise; p.keys = make_philox_keys(seed); p.offset = offset;
     if (out_mode == JF_OUT_INT8) {
         if (!dx8 || !sdx) return JF_ERR_NULL;
         if (!aligned16(dx8)) return JF_ERR_ALIGN;

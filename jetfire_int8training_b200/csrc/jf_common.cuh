@@ -53,11 +53,37 @@ __device__ __forceinline__ float half_to_noise(uint32_t w, int hi) {
     return __fmaf_rn(__uint_as_float(bits), 1.52587890625e-05f, -128.5f);
 }
 
+// The ten round keys of Philox4x32-10 for one seed (key schedule: k + r * (0x9E3779B9, 0xBB67AE85)), computed on the host and
+// passed with the kernel parameters: in the kernel they are constant-bank operands of the round's XOR, which saves the 18
+// additions of the schedule per call (a call serves only 8 elements, so the generator is a large part of every stochastic kernel).
+struct PhiloxKeys {
+    uint32_t k[20];
+};
+inline PhiloxKeys make_philox_keys(uint64_t seed) {
+    PhiloxKeys ks;
+    uint32_t kx = (uint32_t)seed, ky = (uint32_t)(seed >> 32);
+    for (int r = 0; r < 10; ++r) {
+        ks.k[2 * r] = kx;
+        ks.k[2 * r + 1] = ky;
+        kx += 0x9E3779B9u;
+        ky += 0xBB67AE85u;
+    }
+    return ks;
+}
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, const PhiloxKeys& ks) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ ks.k[2 * r], lo1, hi0 ^ c.w ^ ks.k[2 * r + 1], lo0);
+    }
+    return c;
+}
+
 // Noise for the 8 consecutive elements starting at linear index e (e % 8 == 0).
-__device__ __forceinline__ void philox_noise8(uint64_t e, uint64_t seed, uint64_t offset, float out[8]) {
+__device__ __forceinline__ void philox_noise8(uint64_t e, const PhiloxKeys& keys, uint64_t offset, float out[8]) {
     const uint64_t g = e >> 3;
-    const uint4 w = philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), (uint32_t)offset, (uint32_t)(offset >> 32)),
-                                  make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    const uint4 w = philox4x32_10(make_uint4((uint32_t)g, (uint32_t)(g >> 32), (uint32_t)offset, (uint32_t)(offset >> 32)), keys);
     out[0] = half_to_noise(w.x, 0); out[1] = half_to_noise(w.x, 1);
     out[2] = half_to_noise(w.y, 0); out[3] = half_to_noise(w.y, 1);
     out[4] = half_to_noise(w.z, 0); out[5] = half_to_noise(w.z, 1);

@@ -121,8 +121,10 @@ __device__ __forceinline__ float col_sum(float a) {
 
 struct SrCfg {
     const float* noise;
-    uint64_t seed, offset;
+    uint64_t offset;
+    PhiloxKeys keys;
 };
+static inline SrCfg make_sr(const float* noise, uint64_t seed, uint64_t offset) { return SrCfg{noise, offset, make_philox_keys(seed)}; }
 
 // low bytes of four registers -> one word
 __device__ __forceinline__ uint32_t gather_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -196,8 +198,8 @@ __device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const
                         nz[4 * k] = n4.x; nz[4 * k + 1] = n4.y; nz[4 * k + 2] = n4.z; nz[4 * k + 3] = n4.w;
                     }
                 } else {
-                    philox_noise8((uint64_t)(row * N + t.col), sr.seed, sr.offset, &nz[0]);
-                    philox_noise8((uint64_t)(row * N + t.col) + 8, sr.seed, sr.offset, &nz[8]);
+                    philox_noise8((uint64_t)(row * N + t.col), sr.keys, sr.offset, &nz[0]);
+                    philox_noise8((uint64_t)(row * N + t.col) + 8, sr.keys, sr.offset, &nz[8]);
                 }
             }
 #pragma unroll
@@ -342,7 +344,7 @@ __device__ __forceinline__ void widen16(const uint4 (&d)[2], float (&v)[16], __n
 // for the quantisation, which is cheaper than holding 64 fp32 values next to the prefetched next tile.
 // =========================================================================================================
 template <typename T, int TW, bool SR, bool TRANSPOSE>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : 2)
 quantize_kernel(const T* __restrict__ x, int64_t M, int64_t N, int8_t* __restrict__ q, __half* __restrict__ s,
                 int8_t* __restrict__ qt, SrCfg sr) {
     constexpr int NP = Geo<TW>::NP;
@@ -501,7 +503,7 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
             for (int i = 0; i < NP; ++i) lookup16(lut_b, r.d[i], v[i]);
             const float amax = __fadd_rn(block_max<TW>(absmax_tile<NP>(v)), 5e-5f);
             const float scale32 = __fdiv_rn(amax, 127.0f);
-            SrCfg sr{nullptr, 0, 0};
+            SrCfg sr{};
             emit_quantized<TW, false, false, false>([&](int i, float (&a)[16]) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) a[j] = v[i][j];
@@ -589,7 +591,7 @@ ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
                 for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(__fmul_rn(__fsub_rn(f[j], mu), rs), gm[j]);
             }
             const float scale32 = __fdiv_rn(block_max<TW>(absmax_tile<NP>(v)), 127.0f);
-            SrCfg sr{nullptr, 0, 0};
+            SrCfg sr{};
             emit_quantized<TW, false, false, false>([&](int i, float (&a)[16]) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) a[j] = v[i][j];
@@ -686,65 +688,82 @@ __global__ void ln_bwd_dw_kernel(const float* __restrict__ partial, int64_t rows
 // =========================================================================================================
 // residual add (+ optional row statistics): y = x1 + q2*s2 (fp32); store y; block quantise y by truncation
 // =========================================================================================================
-template <typename T, bool MEANVAR, bool SR>
-__global__ void __launch_bounds__(THREADS, 1)
+// Tile width TW (32 by default: 70-80 registers, three CTAs per SM; the first version used one 32x128 tile per warp at 186
+// registers and one CTA per SM and was latency-bound).  With MEANVAR a warp walks the 128/TW tiles of one 128-column slab and
+// writes one partial sum / sum of squares per row and slab, so the workspace layout does not depend on TW.
+template <typename T, bool MEANVAR, bool SR, int TW = 32>
+__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : (TW == 64 ? 2 : 1))
 add_kernel(const T* __restrict__ x1, const int8_t* __restrict__ q2, const __half* __restrict__ s2, int64_t M, int64_t N,
            float* __restrict__ y1, int8_t* __restrict__ qy, __half* __restrict__ sy, float* __restrict__ part_sum,
            float* __restrict__ part_sq, SrCfg sr) {
-    constexpr int TW = 128, NP = Geo<TW>::NP;
-    const int64_t tiles_n_ = (N + TW - 1) / TW;
-    const int64_t tile_ = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
-    if (tile_ >= (M / QB) * tiles_n_) return;
-    const Tile t = make_tile<TW>(tile_, tiles_n_, N);
-    int4 raw[NP];
-    load_rows<TW>(q2, t, N, raw);
-    const float sc = load_scale(s2, t, N);
-    const int64_t tiles_n = (N + TW - 1) / TW;
-    float v[NP][16];
+    constexpr int NP = Geo<TW>::NP;
+    constexpr int SUBS = MEANVAR ? 128 / TW : 1;              // tiles per work item
+    const int64_t tiles_n = (N + TW - 1) / TW;                // tiles per row of tiles
+    const int64_t groups_n = (tiles_n + SUBS - 1) / SUBS;     // work items per row of tiles (MEANVAR: 128-column slabs)
+    const int64_t item = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (item >= (M / QB) * groups_n) return;
+    const int64_t tm = item / groups_n, grp = item % groups_n;
+    float ps[NP], pq[NP];
 #pragma unroll
-    for (int i = 0; i < NP; ++i) {
-        if (t.active) {
-            Load16<T>::load(x1 + row_of<TW>(t, i) * N + t.col, v[i]);
-        } else {
+    for (int i = 0; i < NP; ++i) ps[i] = pq[i] = 0.f;
+#pragma unroll 1
+    for (int sub = 0; sub < SUBS; ++sub) {
+        const int64_t tn = grp * SUBS + sub;
+        if (tn >= tiles_n) break;                             // warp-uniform
+        const Tile t = make_tile<TW>(tm * tiles_n + tn, tiles_n, N);
+        int4 raw[NP];
+        load_rows<TW>(q2, t, N, raw);
+        const float sc = load_scale(s2, t, N);
+        float v[NP][16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
-        }
-    }
+        for (int i = 0; i < NP; ++i) {
+            if (t.active) {
+                Load16<T>::load(x1 + row_of<TW>(t, i) * N + t.col, v[i]);
+            } else {
 #pragma unroll
-    for (int i = 0; i < NP; ++i) {
-        const int64_t row = row_of<TW>(t, i);
-        float f[16];
-        unpack16(raw[i], f);
-        float ps = 0.f, pq = 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float y = __fadd_rn(v[i][j], __fmul_rn(f[j], sc));
-            v[i][j] = y;
-            if (MEANVAR) {
-                ps = __fadd_rn(ps, y);
-                pq = __fadd_rn(pq, __fmul_rn(y, y));
+                for (int j = 0; j < 16; ++j) v[i][j] = 0.f;
             }
         }
-        if (t.active) {
-            float4* dst = reinterpret_cast<float4*>(y1 + row * N + t.col);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) dst[k] = make_float4(v[i][4 * k], v[i][4 * k + 1], v[i][4 * k + 2], v[i][4 * k + 3]);
+        for (int i = 0; i < NP; ++i) {
+            const int64_t row = row_of<TW>(t, i);
+            float f[16];
+            unpack16(raw[i], f);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float y = __fadd_rn(v[i][j], __fmul_rn(f[j], sc));
+                v[i][j] = y;
+                if (MEANVAR) {
+                    ps[i] = __fadd_rn(ps[i], y);
+                    pq[i] = __fadd_rn(pq[i], __fmul_rn(y, y));
+                }
+            }
+            if (t.active) {
+                float4* dst = reinterpret_cast<float4*>(y1 + row * N + t.col);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) dst[k] = make_float4(v[i][4 * k], v[i][4 * k + 1], v[i][4 * k + 2], v[i][4 * k + 3]);
+            }
         }
-        if (MEANVAR) {
-            ps = row_sum<TW>(ps);
-            pq = row_sum<TW>(pq);
-            if (t.cc == 0) {
-                part_sum[row * tiles_n + t.tn] = ps;
-                part_sq[row * tiles_n + t.tn] = pq;
+        const float amax = block_max<TW>(absmax_tile<NP>(v));
+        const float scale32 = __fdiv_rn(amax, 127.0f);
+        emit_quantized<TW, true, SR, false>([&](int i, float (&a)[16]) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) a[j] = v[i][j];
+        }, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+    }
+    if (MEANVAR) {
+        const int lane = threadIdx.x & 31;
+        const int rg = lane / Geo<TW>::LPR, cc = lane % Geo<TW>::LPR;
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const float a = row_sum<TW>(ps[i]), b2 = row_sum<TW>(pq[i]);
+            if (cc == 0) {
+                const int64_t row = tm * QB + i * Geo<TW>::RPP + rg;
+                part_sum[row * groups_n + grp] = a;
+                part_sq[row * groups_n + grp] = b2;
             }
         }
     }
-    const float amax = block_max<TW>(absmax_tile<NP>(v));
-    const float scale32 = __fdiv_rn(amax, 127.0f);
-    emit_quantized<TW, true, SR, false>([&](int i, float (&a)[16]) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) a[j] = v[i][j];
-    }, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
 }
 
 // mean = sum/N; rstd = 1/sqrt(sumsq/N - mean^2)
@@ -815,10 +834,14 @@ static int compute_tw() {
         if (compute_tw() == 32) { CALL32; } else if (compute_tw() == 64) { CALL64; } else { CALL128; } \
     } while (0)
 
+static bool quant_tw32() {
+    static const bool v = [] { const char* e = getenv("JF_QUANT_TW"); return e && atoi(e) == 32; }();
+    return v;
+}
 template <typename T, int TW>
 static void launch_quantize(const void* x, int64_t M, int64_t N, int8_t* q, __half* s, int8_t* qt, bool stochastic, SrCfg sr,
                             cudaStream_t st) {
-    const unsigned grid = grid_for<TW>(M, N, persistent_ctas());
+    const unsigned grid = grid_for<TW>(M, N, TW == 32 ? persistent_ctas() * 3 / 2 : persistent_ctas());
     const T* xp = (const T*)x;
     if (qt) {
         if (stochastic) quantize_kernel<T, TW, true, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
@@ -832,11 +855,11 @@ static void launch_quantize(const void* x, int64_t M, int64_t N, int8_t* q, __ha
 template <typename T>
 static void launch_add(const void* x1, const int8_t* q2, const __half* s2, int64_t M, int64_t N, float* y1, int8_t* qy, __half* sy,
                        float* ps, float* pq, bool meanvar, bool stochastic, SrCfg sr, cudaStream_t st) {
-    const unsigned grid = grid_for<128>(M, N);
+    // work items: 32-column tiles, or (with row statistics) 128-column slabs walked by one warp each
     const T* xp = (const T*)x1;
-    if (meanvar) add_kernel<T, true, false><<<grid, THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
-    else if (stochastic) add_kernel<T, false, true><<<grid, THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
-    else add_kernel<T, false, false><<<grid, THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
+    if (meanvar) add_kernel<T, true, false><<<grid_for<128>(M, N), THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
+    else if (stochastic) add_kernel<T, false, true><<<grid_for<32>(M, N), THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
+    else add_kernel<T, false, false><<<grid_for<32>(M, N), THREADS, 0, st>>>(xp, q2, s2, M, N, y1, qy, sy, ps, pq, sr);
 }
 
 extern "C" {
@@ -865,13 +888,16 @@ int jf_int8_quantize(const void* x, int x_dtype, int64_t M, int64_t N, int8_t* q
     if (qt) JF_REQUIRE_ALIGNED(qt);
     if (noise) JF_REQUIRE_ALIGNED(noise);
     cudaStream_t st = (cudaStream_t)stream;
-    SrCfg sr{noise, seed, offset};
+    SrCfg sr = make_sr(noise, seed, offset);
     __half* sh = (__half*)s;
     const bool sto = stochastic != 0;
     switch (x_dtype) {
-        case JF_F32: JF_TW_DISPATCH((launch_quantize<float, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<float, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
-        case JF_F16: JF_TW_DISPATCH((launch_quantize<__half, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__half, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
-        case JF_BF16: JF_TW_DISPATCH((launch_quantize<__nv_bfloat16, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__nv_bfloat16, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
+        case JF_F32: if (!qt && quant_tw32()) { launch_quantize<float, 32>(x, M, N, q, sh, qt, sto, sr, st); break; }
+                     JF_TW_DISPATCH((launch_quantize<float, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<float, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
+        case JF_F16: if (!qt && quant_tw32()) { launch_quantize<__half, 32>(x, M, N, q, sh, qt, sto, sr, st); break; }
+                     JF_TW_DISPATCH((launch_quantize<__half, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__half, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
+        case JF_BF16: if (!qt && quant_tw32()) { launch_quantize<__nv_bfloat16, 32>(x, M, N, q, sh, qt, sto, sr, st); break; }
+                      JF_TW_DISPATCH((launch_quantize<__nv_bfloat16, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__nv_bfloat16, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
         default: return JF_ERR_DTYPE;
     }
     return check_launch();
@@ -914,7 +940,7 @@ int jf_int8_gelu_backward(const int8_t* qx, const void* sx, const int8_t* qg, co
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qg); JF_REQUIRE_ALIGNED(qd);
     if (noise) JF_REQUIRE_ALIGNED(noise);
-    SrCfg sr{noise, seed, offset};
+    SrCfg sr = make_sr(noise, seed, offset);
     cudaStream_t st = (cudaStream_t)stream;
     const __half* sxh = (const __half*)sx; const __half* sgh = (const __half*)sg; __half* sdh = (__half*)sd;
     if (stochastic) {
@@ -954,7 +980,7 @@ int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* q
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qg); JF_REQUIRE_ALIGNED(qd); JF_REQUIRE_ALIGNED(gamma); JF_REQUIRE_ALIGNED(scratch);
     if (noise) JF_REQUIRE_ALIGNED(noise);
     cudaStream_t st = (cudaStream_t)stream;
-    SrCfg sr{noise, seed, offset};
+    SrCfg sr = make_sr(noise, seed, offset);
     const unsigned grid = grid_for<128>(M, N);
     if (stochastic)
         ln_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
@@ -997,13 +1023,13 @@ static int add_impl(const void* x1, int x1_dtype, const int8_t* q2, const void* 
 
 int jf_int8_add(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1, int8_t* qy, void* sy,
                 int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream) {
-    SrCfg sr{noise, seed, offset};
+    SrCfg sr = make_sr(noise, seed, offset);
     return add_impl(x1, x1_dtype, q2, s2, M, N, y1, qy, sy, nullptr, nullptr, nullptr, false, stochastic != 0, sr, (cudaStream_t)stream);
 }
 
 int jf_int8_add_meanvar(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N, float* y1, int8_t* qy,
                         void* sy, float* mean, float* rstd, float* scratch, void* stream) {
-    SrCfg sr{nullptr, 0, 0};
+    SrCfg sr{};
     return add_impl(x1, x1_dtype, q2, s2, M, N, y1, qy, sy, mean, rstd, scratch, true, false, sr, (cudaStream_t)stream);
 }
 
