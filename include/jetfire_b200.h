@@ -80,7 +80,8 @@ int jf_int8_layernorm_forward(const int8_t* qx, const void* sx, const float* gam
 /* int8_layernorm_backward(x, sx, g, sg, w, QB, m, v, stochastic, eps)   Jetfire/Nonlinear/layernorm.py:467-526
  * (kernels :197-402 and :404-428).  qd/sd: quantised dx; dgamma: fp32 [N].
  * slab: width of the column slab over which the two row reductions of dx are taken; the reference uses 128
- * (its tile width) although it divides by N; pass 128 for reference behaviour.  N must be a multiple of slab.
+ * (its tile width) although it divides by N; pass 128 for reference behaviour.  The reference needs N to be a multiple
+ * of the slab; here the last slab may be shorter (N only has to be a multiple of 32, e.g. 1600).
  * scratch: fp32 [(M/32) * N] workspace for the per-32-row partial sums of dgamma (contents on return unspecified). */
 int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* qg, const void* sg, const float* gamma,
                                const float* mean, const float* rstd, int64_t M, int64_t N, int slab, int8_t* qd, void* sd,

@@ -266,10 +266,14 @@ def int8_layernorm_backward(qx, sx, qg, sg, gamma, mean, rstd, noise=None, slab=
     xhat = ((x - m16).astype(f16) * r16).astype(f16)
     wdy = (gamma.astype(f32)[None, :] * dy.astype(f32)).astype(f32)
     xw = (xhat.astype(f32) * wdy).astype(f32)
-    c1 = (xw.reshape(M, N // slab, slab).sum(-1, dtype=f32) / f32(N)).astype(f32)
-    c2 = (wdy.reshape(M, N // slab, slab).sum(-1, dtype=f32) / f32(N)).astype(f32)
-    c1 = np.repeat(c1, slab, axis=1)
-    c2 = np.repeat(c2, slab, axis=1)
+    # The reference needs N % 128 == 0 (layernorm.py:482, 515); for other N (multiples of 32, e.g. GPT-2 XL's 1600) the last
+    # slab is simply shorter -- modelled by zero padding, which does not change the sums.
+    nsl = -(-N // slab)
+    pad = nsl * slab - N
+    c1 = (np.pad(xw, ((0, 0), (0, pad))).reshape(M, nsl, slab).sum(-1, dtype=f32) / f32(N)).astype(f32)
+    c2 = (np.pad(wdy, ((0, 0), (0, pad))).reshape(M, nsl, slab).sum(-1, dtype=f32) / f32(N)).astype(f32)
+    c1 = np.repeat(c1, slab, axis=1)[:, :N]
+    c2 = np.repeat(c2, slab, axis=1)[:, :N]
     t = ((xhat.astype(f32) * c1).astype(f32) + c2).astype(f32)
     dx = (((wdy - t).astype(f32)) * r16.astype(f32)).astype(f32).astype(f16)
     amax16 = np.abs(_blk(dx)).max(axis=(1, 3))

@@ -154,7 +154,7 @@ def test_gelu_vs_oracle(NL, oracle, M, N):
     assert_payload_close(n(q), qo, 2e-3, "gelu_bwd"); assert_scales_close(n(s), so, 1)
 
 
-@pytest.mark.parametrize("M,N", [(64, 128), (256, 768), (128, 3072)])
+@pytest.mark.parametrize("M,N", [(64, 128), (256, 768), (128, 3072), (64, 160), (96, 1600)])
 def test_layernorm_vs_oracle(NL, oracle, M, N):
     g = torch.Generator().manual_seed(N + 1)
     xf = outlier_randn(g, M, N)

@@ -96,10 +96,12 @@ def int8_layernorm_backward(x, sx, g, sg, w, B, m, v, stochastic=False, eps=1e-6
     dy = _deq(g2, sg2, half_product=True).half()
     xhat = ((xv - mu) * rs).float()
     wdy = w.float() * dy.float()
-    slab = 128 if N % 128 == 0 else N
-    c1 = (xhat * wdy).reshape(M, N // slab, slab).sum(-1, keepdim=True) / N
-    c2 = wdy.reshape(M, N // slab, slab).sum(-1, keepdim=True) / N
-    dx = ((wdy.reshape(M, N // slab, slab) - (xhat.reshape(M, N // slab, slab) * c1 + c2)) * rs.float().reshape(M, 1, 1)).reshape(M, N)
+    slab = 128
+    pad = (-N) % slab
+    padded = lambda a: torch.nn.functional.pad(a, (0, pad)).reshape(M, -1, slab)      # a shorter last slab = zero padding
+    c1 = padded(xhat * wdy).sum(-1, keepdim=True) / N
+    c2 = padded(wdy).sum(-1, keepdim=True) / N
+    dx = ((padded(wdy) - (padded(xhat) * c1 + c2)) * rs.float().reshape(M, 1, 1)).reshape(M, -1)[:, :N]
     dx = dx.half().float()
     dw = (dy.float() * xhat).sum(0)
     q, s = _quant(dx, stochastic)
