@@ -603,17 +603,26 @@ ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
 // LayerNorm backward (dx and per-32-row partial dgamma), row reductions over the tile's 128-column slab.
 // Rounding points of the reference: mean, rstd, x, dy, xhat in fp16; c1, c2 and the dx expression in fp32; dx -> fp16.
 // =========================================================================================================
+// Two warps share one 32x128 slab tile, 64 columns each (64 values per lane instead of 128: 2 CTAs per SM instead of one
+// at 242 registers).  The quantisation blocks and the dgamma columns are private to a warp; only the two row sums per row cross
+// the warps, through shared memory and a 64-thread named barrier per row pass.  The sum order is the one of a single warp over
+// 8 lanes: ((l0+l1)+(l2+l3)) + ((l4+l5)+(l6+l7)).
 template <bool SR>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
               const __half* __restrict__ sg, const float* __restrict__ gamma, const float* __restrict__ mean,
               const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd,
               float* __restrict__ dw_partial, SrCfg sr) {
-    constexpr int TW = 128, NP = Geo<TW>::NP;
-    const int64_t tiles_n_ = (N + TW - 1) / TW;
-    const int64_t tile_ = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
-    if (tile_ >= (M / QB) * tiles_n_) return;
-    const Tile t = make_tile<TW>(tile_, tiles_n_, N);
+    constexpr int TW = 64, NP = Geo<TW>::NP, PAIRS = WARPS / 2;
+    __shared__ float2 row_part[PAIRS][2][QB];          // [pair][half][row of the tile] = (sum xhat*wdy, sum wdy) over the half
+    const int warp = threadIdx.x >> 5, pair = warp >> 1, half = warp & 1;
+    const int64_t slabs_n = (N + 127) / 128, tiles_n_ = (N + TW - 1) / TW;
+    const int64_t slab_tile = (int64_t)blockIdx.x * PAIRS + pair;          // index of the 32 x 128 slab tile
+    if (slab_tile >= (M / QB) * slabs_n) return;                           // both warps of a pair leave together
+    const int64_t tm_ = slab_tile / slabs_n, tn_ = (slab_tile % slabs_n) * 2 + half;
+    // the right half of a short last slab may lie outside the tensor: such a warp loads zeros and only takes part in the sums
+    Tile t = make_tile<TW>(tm_ * tiles_n_ + (tn_ < tiles_n_ ? tn_ : tiles_n_ - 1), tiles_n_, N);
+    if (tn_ >= tiles_n_) t.active = false;
     int4 rx[NP], rgr[NP];
     load_rows<TW>(qx, t, N, rx);
     load_rows<TW>(qg, t, N, rgr);
@@ -633,6 +642,7 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
 #pragma unroll
     for (int i = 0; i < NP; ++i) {
         const int64_t row = row_of<TW>(t, i);
+        const int row_in_tile = i * Geo<TW>::RPP + t.rg;
         const __half2 mu2 = __half2half2(__float2half_rn(__ldg(mean + row)));
         const __half rs16 = __float2half_rn(__ldg(rstd + row));
         const __half2 rs2 = __half2half2(rs16);
@@ -653,7 +663,13 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
             s2 = __fadd_rn(__fadd_rn(s2, wdy[2 * j]), wdy[2 * j + 1]);
             dwp[2 * j] = __fadd_rn(dwp[2 * j], pr.x); dwp[2 * j + 1] = __fadd_rn(dwp[2 * j + 1], pr.y);
         }
-        const float c1 = __fdiv_rn(row_sum<TW>(s1), n_f), c2 = __fdiv_rn(row_sum<TW>(s2), n_f);
+        // sums over this warp's 64 columns, then the other warp's through shared memory (left + right)
+        s1 = row_sum<TW>(s1);
+        s2 = row_sum<TW>(s2);
+        if (t.cc == 0) row_part[pair][half][row_in_tile] = make_float2(s1, s2);
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+        const float2 lft = row_part[pair][0][row_in_tile], rgt = row_part[pair][1][row_in_tile];
+        const float c1 = __fdiv_rn(__fadd_rn(lft.x, rgt.x), n_f), c2 = __fdiv_rn(__fadd_rn(lft.y, rgt.y), n_f);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float tt = __fadd_rn(__fmul_rn(xh[j], c1), c2);
@@ -676,13 +692,23 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
     }, scale32, t, M, N, qd, sd, sr, nullptr, nullptr);
 }
 
-// dgamma[n] = sum over the M/32 partial rows, ascending
-__global__ void ln_bwd_dw_kernel(const float* __restrict__ partial, int64_t rows, int64_t N, float* __restrict__ dgamma) {
-    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
+// dgamma[n] = sum over the M/32 partial rows: 8 interleaved row groups per column (thread (x, g) sums rows g, g+8, ...), then the
+// 8 group sums in ascending order -- a fixed order, so the result is deterministic.  Block = 32 columns x 8 groups.
+__global__ void __launch_bounds__(256) ln_bwd_dw_kernel(const float* __restrict__ partial, int64_t rows, int64_t N, float* __restrict__ dgamma) {
+    __shared__ float red[8][32];
+    const int tx = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int64_t n = (int64_t)blockIdx.x * 32 + tx;
     float a = 0.f;
-    for (int64_t r = 0; r < rows; ++r) a = __fadd_rn(a, partial[r * N + n]);
-    dgamma[n] = a;
+    if (n < N)
+        for (int64_t r = g; r < rows; r += 8) a = __fadd_rn(a, partial[r * N + n]);
+    red[g][tx] = a;
+    __syncthreads();
+    if (g == 0 && n < N) {
+        float s = red[0][tx];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) s = __fadd_rn(s, red[k][tx]);
+        dgamma[n] = s;
+    }
 }
 
 // =========================================================================================================
@@ -980,13 +1006,14 @@ int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* q
     if (noise) JF_REQUIRE_ALIGNED(noise);
     cudaStream_t st = (cudaStream_t)stream;
     SrCfg sr = make_sr(noise, seed, offset);
-    const unsigned grid = grid_for<128>(M, N);
+    const int64_t slab_tiles = (M / QB) * ((N + 127) / 128);
+    const unsigned grid = (unsigned)((slab_tiles + WARPS / 2 - 1) / (WARPS / 2));   // two warps per 32 x 128 slab tile
     if (stochastic)
         ln_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
     else
         ln_bwd_kernel<false><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
     if (int e = check_launch()) return e;
-    ln_bwd_dw_kernel<<<(unsigned)((N + 127) / 128), 128, 0, st>>>(scratch, M / QB, N, dgamma);
+    ln_bwd_dw_kernel<<<(unsigned)((N + 31) / 32), 256, 0, st>>>(scratch, M / QB, N, dgamma);
     return check_launch();
 }
 
