@@ -607,19 +607,19 @@ ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
 // at 242 registers).  The quantisation blocks and the dgamma columns are private to a warp; only the two row sums per row cross
 // the warps, through shared memory and a 64-thread named barrier per row pass.  The sum order is the one of a single warp over
 // 8 lanes: ((l0+l1)+(l2+l3)) + ((l4+l5)+(l6+l7)).
-template <bool SR>
-__global__ void __launch_bounds__(THREADS, 2)
+template <bool SR, int TW = 64>
+__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : 2)
 ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
               const __half* __restrict__ sg, const float* __restrict__ gamma, const float* __restrict__ mean,
               const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd,
               float* __restrict__ dw_partial, SrCfg sr) {
-    constexpr int TW = 64, NP = Geo<TW>::NP, PAIRS = WARPS / 2;
-    __shared__ float2 row_part[PAIRS][2][QB];          // [pair][half][row of the tile] = (sum xhat*wdy, sum wdy) over the half
-    const int warp = threadIdx.x >> 5, pair = warp >> 1, half = warp & 1;
+    constexpr int NP = Geo<TW>::NP, WPS = 128 / TW, PAIRS = WARPS / WPS;   // WPS warps per slab tile, PAIRS slab tiles per CTA
+    __shared__ float2 row_part[PAIRS][WPS][QB];        // [slab tile][part][row of the tile] = (sum xhat*wdy, sum wdy) over the part
+    const int warp = threadIdx.x >> 5, pair = warp / WPS, half = warp % WPS;
     const int64_t slabs_n = (N + 127) / 128, tiles_n_ = (N + TW - 1) / TW;
     const int64_t slab_tile = (int64_t)blockIdx.x * PAIRS + pair;          // index of the 32 x 128 slab tile
     if (slab_tile >= (M / QB) * slabs_n) return;                           // both warps of a pair leave together
-    const int64_t tm_ = slab_tile / slabs_n, tn_ = (slab_tile % slabs_n) * 2 + half;
+    const int64_t tm_ = slab_tile / slabs_n, tn_ = (slab_tile % slabs_n) * WPS + half;
     // the right half of a short last slab may lie outside the tensor: such a warp loads zeros and only takes part in the sums
     Tile t = make_tile<TW>(tm_ * tiles_n_ + (tn_ < tiles_n_ ? tn_ : tiles_n_ - 1), tiles_n_, N);
     if (tn_ >= tiles_n_) t.active = false;
@@ -667,9 +667,17 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
         s1 = row_sum<TW>(s1);
         s2 = row_sum<TW>(s2);
         if (t.cc == 0) row_part[pair][half][row_in_tile] = make_float2(s1, s2);
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
-        const float2 lft = row_part[pair][0][row_in_tile], rgt = row_part[pair][1][row_in_tile];
-        const float c1 = __fdiv_rn(__fadd_rn(lft.x, rgt.x), n_f), c2 = __fdiv_rn(__fadd_rn(lft.y, rgt.y), n_f);
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + pair), "n"(32 * WPS) : "memory");
+        float2 tot;
+        {
+            const float2 lft = row_part[pair][0][row_in_tile], rgt = row_part[pair][1][row_in_tile];
+            tot = make_float2(__fadd_rn(lft.x, rgt.x), __fadd_rn(lft.y, rgt.y));
+            if (WPS == 4) {
+                const float2 l2 = row_part[pair][2][row_in_tile], r2 = row_part[pair][3][row_in_tile];
+                tot = make_float2(__fadd_rn(tot.x, __fadd_rn(l2.x, r2.x)), __fadd_rn(tot.y, __fadd_rn(l2.y, r2.y)));
+            }
+        }
+        const float c1 = __fdiv_rn(tot.x, n_f), c2 = __fdiv_rn(tot.y, n_f);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float tt = __fadd_rn(__fmul_rn(xh[j], c1), c2);
@@ -1007,11 +1015,16 @@ int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* q
     cudaStream_t st = (cudaStream_t)stream;
     SrCfg sr = make_sr(noise, seed, offset);
     const int64_t slab_tiles = (M / QB) * ((N + 127) / 128);
-    const unsigned grid = (unsigned)((slab_tiles + WARPS / 2 - 1) / (WARPS / 2));   // two warps per 32 x 128 slab tile
-    if (stochastic)
-        ln_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
-    else
-        ln_bwd_kernel<false><<<grid, THREADS, 0, st>>>(qx, (const __half*)sx, qg, (const __half*)sg, gamma, mean, rstd, M, N, qd, (__half*)sd, scratch, sr);
+    static const int wps = [] { const char* e = getenv("JF_LNB_TW"); return (e && atoi(e) == 32) ? 4 : 2; }();   // warps per slab tile
+    const unsigned grid = (unsigned)((slab_tiles + WARPS / wps - 1) / (WARPS / wps));
+    const __half* sxh = (const __half*)sx; const __half* sgh = (const __half*)sg; __half* sdh = (__half*)sd;
+    if (wps == 4) {
+        if (stochastic) ln_bwd_kernel<true, 32><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
+        else ln_bwd_kernel<false, 32><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
+    } else {
+        if (stochastic) ln_bwd_kernel<true, 64><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
+        else ln_bwd_kernel<false, 64><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
+    }
     if (int e = check_launch()) return e;
     ln_bwd_dw_kernel<<<(unsigned)((N + 31) / 32), 256, 0, st>>>(scratch, M / QB, N, dgamma);
     return check_launch();
