@@ -530,6 +530,19 @@ def run_gpt2(args):
                           "config": {"workload": f"GPT-2 {args.model} INT8 training step", "n_layer": cfg.n_layer, "n_embd": cfg.n_embd,
                                      "micro_batch": mb, "seq_len": T, "params": model.num_params(), "parallelism": f"dp{world}"},
                           "loss_first": losses[0], "loss_last": float(loss)}), flush=True)
+    if args.kernel_table and rank == 0:
+        # device time per kernel over three more steps (torch.profiler, CUDA activity), largest first
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            for _ in range(3):
+                step(*batch())
+            torch.cuda.synchronize()
+        rows = sorted(((e.device_time_total, e.count, e.key) for e in prof.key_averages()
+                       if e.device_time_total > 0 and e.device_type.name == "CUDA"), reverse=True)
+        tot = sum(r[0] for r in rows)
+        print(f"device time per step: {tot / 3:.1f} us", flush=True)
+        for t, c, k in rows[:32]:
+            print(f"{t / 3:10.1f} us/step {100 * t / tot:5.1f} %  x{c // 3:4d}  {k[:120]}", flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -626,6 +639,7 @@ def main():
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the linear workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (kernel tuning runs)")
+    ap.add_argument("--kernel-table", action="store_true", help="gpt2 workload: also print the device time per kernel")
     ap.add_argument("--op", default=None, help="nonlinear workload: run only this operator (profiling)")
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=3072)
