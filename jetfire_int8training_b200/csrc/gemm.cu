@@ -27,6 +27,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "jf_common.cuh"
 #include "ptx_sm100.cuh"
@@ -216,31 +217,46 @@ __device__ __forceinline__ void store_block(const GemmParams& p, const float (&a
         const Divisor d = make_divisor(amax);
         const bool zero = (amax == 0.f);
         uint32_t words[8];
+        // One decision per warp each: the exact-quotient fast path is valid for the whole block (same divisor in every lane),
+        // and only stochastic rounding can leave [-127, 127] (127 + noise -> 128), so only it needs the clamp.
+        const bool fast = __all_sync(0xffffffffu, d.fast || zero);
+        auto quantise_all = [&](auto fast_c, auto sr_c) {
+            constexpr bool FAST = decltype(fast_c)::value, SRND = decltype(sr_c)::value;
 #pragma unroll
-        for (int k8 = 0; k8 < 4; ++k8) {      // 8 elements = one Philox call
-            float nz[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (p.stochastic) {
-                if (p.noise) {
-                    const float4 n0 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8));
-                    const float4 n1 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8 + 4));
-                    nz[0] = n0.x; nz[1] = n0.y; nz[2] = n0.z; nz[3] = n0.w; nz[4] = n1.x; nz[5] = n1.y; nz[6] = n1.z; nz[7] = n1.w;
-                } else {
-                    philox_noise8((uint64_t)(row * p.N + col + 8 * k8), p.keys, p.offset, nz);
+            for (int k8 = 0; k8 < 4; ++k8) {      // 8 elements = one Philox call
+                float nz[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (SRND) {
+                    if (p.noise) {
+                        const float4 n0 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8));
+                        const float4 n1 = __ldg(reinterpret_cast<const float4*>(p.noise + row * p.N + col + 8 * k8 + 4));
+                        nz[0] = n0.x; nz[1] = n0.y; nz[2] = n0.z; nz[3] = n0.w; nz[4] = n1.x; nz[5] = n1.y; nz[6] = n1.z; nz[7] = n1.w;
+                    } else {
+                        philox_noise8((uint64_t)(row * p.N + col + 8 * k8), p.keys, p.offset, nz);
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t bts[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float a127 = __fmul_rn(127.0f, ab[8 * k8 + 4 * h + u]);
+                        float v;
+                        if (FAST) {
+                            const float q0 = __fmul_rn(a127, d.inv);
+                            v = __fmaf_rn(__fmaf_rn(-d.b, q0, a127), d.inv, q0);
+                        } else {
+                            v = __fdiv_rn(a127, d.b);
+                        }
+                        if (SRND) v = fminf(fmaxf(__fadd_rn(v, nz[4 * h + u]), -127.f), 127.f);
+                        bts[u] = __float_as_uint(__fadd_rn(v, 12582912.0f));     // round to nearest even; the low byte is the payload
+                    }
+                    words[2 * k8 + h] = zero ? 0u : __byte_perm(__byte_perm(bts[0], bts[1], 0x0040), __byte_perm(bts[2], bts[3], 0x0040), 0x5410);
                 }
             }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t bts[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    float v = div_exact(__fmul_rn(127.0f, ab[8 * k8 + 4 * h + u]), d);
-                    if (p.stochastic) v = __fadd_rn(v, nz[4 * h + u]);
-                    v = fminf(fmaxf(v, -127.f), 127.f);
-                    bts[u] = rne_byte(v);
-                }
-                words[2 * k8 + h] = zero ? 0u : pack4(bts[0], bts[1], bts[2], bts[3]);
-            }
-        }
+        };
+        using T_ = std::true_type; using F_ = std::false_type;
+        if (fast) { if (p.stochastic) quantise_all(T_{}, T_{}); else quantise_all(T_{}, F_{}); }
+        else      { if (p.stochastic) quantise_all(F_{}, T_{}); else quantise_all(F_{}, F_{}); }
         if (p.mode == MODE_INT8) {
             int4* dst = reinterpret_cast<int4*>(p.out8 + row * p.N + col);
             dst[0] = make_int4(words[0], words[1], words[2], words[3]);

@@ -28,13 +28,15 @@ constexpr int RASTER_GM = 16;
 constexpr int EPI_WARPS = 16;                      // consumer warps
 constexpr int NUM_ISSUERS = 2;                     // MMA-issuing warps = accumulator groups
 constexpr int GEMM_THREADS = (EPI_WARPS + 1 + NUM_ISSUERS) * 32;
+// (32-bit arithmetic: the launcher refuses problems with 2^31 tiles or more, and 64-bit divisions cost ~40 instructions each)
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t& tm, int64_t& tn) {
-    const int64_t group_size = RASTER_GM * tiles_n;
-    const int64_t group = tile / group_size, in_group = tile % group_size;
-    const int64_t first_m = group * RASTER_GM;
-    const int64_t gm = min((int64_t)RASTER_GM, tiles_m - first_m);
-    tm = first_m + in_group % gm;
-    tn = in_group / gm;
+    const uint32_t t = (uint32_t)tile, tmx = (uint32_t)tiles_m, tnx = (uint32_t)tiles_n;
+    const uint32_t group_size = RASTER_GM * tnx;
+    const uint32_t group = t / group_size, in_group = t % group_size;
+    const uint32_t first_m = group * RASTER_GM;
+    const uint32_t gm = min((uint32_t)RASTER_GM, tmx - first_m);
+    tm = (int64_t)(first_m + in_group % gm);
+    tn = (int64_t)(in_group / gm);
 }
 
 template <bool A_MN, bool B_MN, int CONV>
@@ -163,10 +165,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             int tm32, tn32, split32;
             {
-                const int64_t tile = item % num_tiles;
+                const uint32_t tile = (uint32_t)item % (uint32_t)num_tiles;
                 int64_t tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-                tm32 = (int)tm; tn32 = (int)tn; split32 = (int)(item / num_tiles);
+                tm32 = (int)tm; tn32 = (int)tn; split32 = (int)((uint32_t)item / (uint32_t)num_tiles);
             }
             const int kb0 = (int)(split32 * p.kb_per_split);
             const int kb1 = (int)min(p.nkb, (int64_t)kb0 + p.kb_per_split);
