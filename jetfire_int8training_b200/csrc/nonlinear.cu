@@ -15,6 +15,7 @@
 // enough loads in flight to approach HBM bandwidth; kernels that need a 128-column slab (LayerNorm backward, residual add with
 // row statistics) use the wide tile.
 #include <cstdlib>
+#include <type_traits>
 
 #include "jf_common.cuh"
 
@@ -179,8 +180,11 @@ __device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const
     constexpr int NP = Geo<TW>::NP;
     const Divisor d = make_divisor(scale32);
     const bool zero = (scale32 == 0.f);
-    // one decision per warp: the Markstein path is exact only inside its exponent window
+    // One decision per warp: the Markstein path is exact only inside its exponent window.  The two paths are separate
+    // instantiations of the loop (a run-time flag inside the element loop keeps both alive for every element).
     const bool fast = __all_sync(0xffffffffu, d.fast || zero);
+    auto rows = [&](auto fast_c) {
+    constexpr bool FAST = decltype(fast_c)::value;
 #pragma unroll
     for (int i = 0; i < NP; ++i) {
         const int64_t row = row_of<TW>(t, i);
@@ -209,7 +213,7 @@ __device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const
                 for (int j = 0; j < 4; ++j) {
                     const float a = av[4 * k + j];
                     float x;
-                    if (fast) {
+                    if (FAST) {
                         const float q0 = __fmul_rn(a, d.inv);
                         x = __fmaf_rn(__fmaf_rn(-d.b, q0, a), d.inv, q0);
                     } else {
@@ -230,6 +234,8 @@ __device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const
             *reinterpret_cast<int4*>(dst) = make_int4(words[0], words[1], words[2], words[3]);
         }
     }
+    };
+    if (fast) rows(std::true_type{}); else rows(std::false_type{});
     if (t.active && t.rg == 0 && (t.cc & 1) == 0) s[t.tm * (N / QB) + (t.col >> 5)] = __float2half_rn(scale32);
     if (TRANSPOSE) {
         __syncwarp();
