@@ -45,8 +45,10 @@ template <int TW>
 __device__ __forceinline__ Tile make_tile(int64_t tile, int64_t tiles_n, int64_t N) {
     Tile t;
     t.lane = threadIdx.x & 31;
-    t.tm = tile / tiles_n;
-    t.tn = tile % tiles_n;
+    // 32-bit division: the entry points refuse tensors with 2^31 blocks or more, and a 64-bit division costs ~40 instructions,
+    // which is noticeable when a lane handles only 32-64 elements per tile
+    t.tm = (int64_t)((uint32_t)tile / (uint32_t)tiles_n);
+    t.tn = (int64_t)((uint32_t)tile % (uint32_t)tiles_n);
     t.rg = t.lane / Geo<TW>::LPR;
     t.cc = t.lane % Geo<TW>::LPR;
     t.row0 = t.tm * QB;
@@ -841,7 +843,10 @@ using namespace jf;
         if (!aligned16(p)) return JF_ERR_ALIGN; \
     } while (0)
 
-static inline int check_mn(int64_t M, int64_t N) { return (mult32(M) && mult32(N)) ? JF_OK : JF_ERR_SHAPE; }
+static inline int check_mn(int64_t M, int64_t N) {
+    // blocks are indexed with 32-bit arithmetic inside the kernels
+    return (mult32(M) && mult32(N) && (M / 32) * (N / 32) < (int64_t(1) << 31)) ? JF_OK : JF_ERR_SHAPE;
+}
 
 // CTAs of a persistent launch: two per SM (the streaming kernels fit two 8-warp CTAs per SM; one that fits only one simply runs
 // its second half afterwards).
