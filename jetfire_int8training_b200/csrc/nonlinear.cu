@@ -627,7 +627,8 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
     const int64_t slabs_n = (N + 127) / 128, tiles_n_ = (N + TW - 1) / TW;
     const int64_t slab_tile = (int64_t)blockIdx.x * PAIRS + pair;          // index of the 32 x 128 slab tile
     if (slab_tile >= (M / QB) * slabs_n) return;                           // both warps of a pair leave together
-    const int64_t tm_ = slab_tile / slabs_n, tn_ = (slab_tile % slabs_n) * WPS + half;
+    const int64_t tm_ = (int64_t)((uint32_t)slab_tile / (uint32_t)slabs_n);                      // 32-bit division
+    const int64_t tn_ = (int64_t)((uint32_t)slab_tile % (uint32_t)slabs_n) * WPS + half;
     // the right half of a short last slab may lie outside the tensor: such a warp loads zeros and only takes part in the sums
     Tile t = make_tile<TW>(tm_ * tiles_n_ + (tn_ < tiles_n_ ? tn_ : tiles_n_ - 1), tiles_n_, N);
     if (tn_ >= tiles_n_) t.active = false;
@@ -744,7 +745,7 @@ add_kernel(const T* __restrict__ x1, const int8_t* __restrict__ q2, const __half
     const int64_t groups_n = (tiles_n + SUBS - 1) / SUBS;     // work items per row of tiles (MEANVAR: 128-column slabs)
     const int64_t item = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
     if (item >= (M / QB) * groups_n) return;
-    const int64_t tm = item / groups_n, grp = item % groups_n;
+    const int64_t tm = (int64_t)((uint32_t)item / (uint32_t)groups_n), grp = (int64_t)((uint32_t)item % (uint32_t)groups_n);   // 32-bit division
     float ps[NP], pq[NP];
 #pragma unroll
     for (int i = 0; i < NP; ++i) ps[i] = pq[i] = 0.f;
