@@ -267,13 +267,25 @@ __device__ __forceinline__ void unpack16(const int4& r, float (&f)[16]) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) f[4 * k + j] = byte_to_float(w[k], j);
 }
+// The 16 payload values of one row chunk as exact fp16 pairs, without a conversion instruction: a byte u = q ^ 0x80 placed under
+// the high byte 0x64 is the half 1024 + u, and (1024 + u) - 1152 = q exactly (two values per prmt and per sub.f16x2).
+__device__ __forceinline__ void unpack16_h2(const int4& r, __half2 (&h)[8]) {
+    const uint32_t w[4] = {(uint32_t)r.x ^ 0x80808080u, (uint32_t)r.y ^ 0x80808080u, (uint32_t)r.z ^ 0x80808080u, (uint32_t)r.w ^ 0x80808080u};
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = __byte_perm(w[k], 0x64646464u, 0x5140), hi = __byte_perm(w[k], 0x64646464u, 0x5342);
+        h[2 * k] = __hsub2_rn(*reinterpret_cast<const __half2*>(&lo), bias);
+        h[2 * k + 1] = __hsub2_rn(*reinterpret_cast<const __half2*>(&hi), bias);
+    }
+}
 // fp16-rounded dequantisation fp32(fp16(q) * s) of one row chunk (the reference's int8 * fp16 product), two values at a time
 __device__ __forceinline__ void dequant16_h(const int4& r, __half2 s2, float (&f)[16]) {
-    float qf[16];
-    unpack16(r, qf);
+    __half2 q2[8];
+    unpack16_h2(r, q2);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        const float2 p = __half22float2(__hmul2_rn(__floats2half2_rn(qf[2 * j], qf[2 * j + 1]), s2));
+        const float2 p = __half22float2(__hmul2_rn(q2[j], s2));
         f[2 * j] = p.x; f[2 * j + 1] = p.y;
     }
 }
@@ -656,14 +668,15 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
         const __half rs16 = __float2half_rn(__ldg(rstd + row));
         const __half2 rs2 = __half2half2(rs16);
         const float rs = __half2float(rs16);
-        float fx[16], fg[16], xh[16], wdy[16];
-        unpack16(rx[i], fx);
-        unpack16(rgr[i], fg);
+        float xh[16], wdy[16];
+        __half2 hx[8], hg[8];
+        unpack16_h2(rx[i], hx);
+        unpack16_h2(rgr[i], hg);
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const __half2 x16 = __hmul2_rn(__floats2half2_rn(fx[2 * j], fx[2 * j + 1]), sx2);
-            const __half2 dy16 = __hmul2_rn(__floats2half2_rn(fg[2 * j], fg[2 * j + 1]), sg2);
+            const __half2 x16 = __hmul2_rn(hx[j], sx2);
+            const __half2 dy16 = __hmul2_rn(hg[j], sg2);
             const __half2 xhat16 = __hmul2_rn(__hsub2_rn(x16, mu2), rs2);
             const float2 xf = __half22float2(xhat16), dyf = __half22float2(dy16), pr = __half22float2(__hmul2_rn(dy16, xhat16));
             xh[2 * j] = xf.x; xh[2 * j + 1] = xf.y;
