@@ -136,7 +136,8 @@ def outlier_randn(g, M, N, frac=0.005, mult=30.0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("JETFIRE_REFERENCE"), required="JETFIRE_REFERENCE" not in os.environ,
+                    help="checkout of thu-ml/Jetfire-INT8Training (or set JETFIRE_REFERENCE)")
     ap.add_argument("--out", default=HERE)
     args = ap.parse_args()
 
