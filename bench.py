@@ -12,6 +12,9 @@ all-reduce per step, which is the data-parallel exchange of the training recipe.
 One JSON line is printed by rank 0.  `value` is whole-job INT8 tensor throughput (10^12 ops/s) with operands resident in
 HBM; `e2e` is the same metric through the public Python API with HOST (pinned) operands and results, copies inside the
 timed region; `roofline` describes the forward GEMM kernel; `cpu_baseline` is the CPU oracle on a bounded sample.
+The same line carries the two other parts of the metric: `gpt2` (GPT-2 124M INT8 training step, micro-batch 12 x 1024 per
+GPU, data-parallel over the N ranks: tokens/s, ms per step, first / last loss) and `nonlinear` (GB/s and fraction of the
+measured HBM bandwidth per nonlinear operator on [8192,768] and [8192,3072], rank 0's GPU); --no-extras skips both.
 `--impl reference` times the reference algorithm's CPU restatement (oracle/) on the host cores.
 """
 import argparse
@@ -129,10 +132,11 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cores = len(os.sched_getaffinity(0))
+    os.environ["OMP_NUM_THREADS"] = str(cores)      # torchrun exports OMP_NUM_THREADS=1: the baseline uses every host core
     from oracle import jetfire_oracle as O
     O.build_c_oracle()
-    cores = len(os.sched_getaffinity(0))
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    cores = O.set_threads(cores)                     # the thread count actually in effect
     Ms, Ns, Ks = 512, 512, 8192
     for _ in range(max(1, min(args.warmup, 1))):
         cpu_linear_sample(O, 256, 256, 1024)
@@ -169,7 +173,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     from jetfire_int8training_b200 import Linear, Nonlinear, rng
-    from jetfire_int8training_b200.dp import allreduce_mean_
+    from jetfire_int8training_b200.dp import OverlappedMeanReducer
     from jetfire_int8training_b200._lib import lib
     L = lib()
     rng.manual_seed(1234 + rank)
@@ -186,6 +190,10 @@ def run_ours(args):
 
     launches_per_step = 3 + (1 if L.jf_igemm_wgrad_plan(N, K, M, 0) > 1 else 0)
     fwd_ev = []
+    # data-parallel exchange: the mean of dW over the ranks, on a side stream.  The weight gradient of step i is consumed by the
+    # optimiser only, so its all-reduce overlaps the forward and input-gradient GEMMs of step i+1; the step waits for the
+    # previous step's collective right after its own weight gradient (and the timed region ends with a wait for the last one).
+    reducer = OverlappedMeanReducer(device=dev)
 
     def step(time_fwd=False):
         if time_fwd:
@@ -195,8 +203,8 @@ def run_ours(args):
         if time_fwd:
             e1.record(); fwd_ev.append((e0, e1))
         gx8, gsx, gw = Linear.int8_linear_backward(X8, SX, G8, SG, None, W8, SW, 32, stochastic=True)
-        if world > 1:
-            allreduce_mean_([gw])
+        reducer.wait()
+        reducer.submit([gw])
         return y8, sy, gx8, gsx, gw
 
     for _ in range(args.warmup):
@@ -214,6 +222,7 @@ def run_ours(args):
     ev0.record()
     for _ in range(args.steps):
         step(time_fwd=True)
+    reducer.wait()                    # the last step's gradient exchange is part of the timed region
     ev1.record()
     torch.cuda.synchronize()
     t_wall1 = time.time()
@@ -244,6 +253,7 @@ def run_ours(args):
     host_in = [t.cpu().pin_memory() for t in (X8, SX, W8, SW, G8, SG)]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     outs = step()
+    reducer.wait()
     host_out = [torch.empty_like(o, device="cpu").pin_memory() for o in outs]
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 
@@ -251,8 +261,8 @@ def run_ours(args):
         x8, sx, w8, sw, g8, sg = [t.to(dev, non_blocking=True) for t in host_in]
         y8, sy = Linear.int8_linear_forward(x8, sx, w8, sw, True, 32)
         gx8, gsx, gw = Linear.int8_linear_backward(x8, sx, g8, sg, None, w8, sw, 32, stochastic=True)
-        if world > 1:
-            allreduce_mean_([gw])
+        reducer.submit([gw])
+        reducer.wait()                # the reduced gradient is what goes back to the host
         for h, o in zip(host_out, (y8, sy, gx8, gsx, gw)):
             h.copy_(o, non_blocking=True)
 
@@ -280,7 +290,10 @@ def run_ours(args):
     # The same step through the package's host pipeline (host_pipeline.LinearStepPipeline): H2D of step i+1 | GEMMs of step i |
     # D2H of step i-1.  Every step still copies all of its inputs in and all of its results out inside the timed region.
     from jetfire_int8training_b200.host_pipeline import LinearStepPipeline
-    pipe = LinearStepPipeline(dev, stochastic=True, after_backward=(lambda gw: allreduce_mean_([gw])) if world > 1 else None)
+    def reduce_now(gw):
+        reducer.submit([gw])
+        reducer.wait()
+    pipe = LinearStepPipeline(dev, stochastic=True, after_backward=reduce_now if world > 1 else None)
 
     def timed_pipeline(nsteps):
         pipe.submit(host_in, host_out, next_host_in=host_in)
@@ -308,6 +321,18 @@ def run_ours(args):
     e2e_val = world * ops_step * e2e_pipe_steps / (e2e_ms * 1e-3) / 1e12
     e2e_serial_val = world * ops_step * e2e_steps / (e2e_serial_ms * 1e-3) / 1e12
 
+    # ---------------- the other two parts of the metric, in the same line
+    gpt2_rec = nonlinear_rec = None
+    if not args.no_extras:
+        del pipe, host_in, host_out, outs, X8, W8, G8
+        torch.cuda.empty_cache()
+        gpt2_rec = gpt2_measure("124M", 0, max(5, min(args.steps, 10)), 3, dev, rank, world, local)
+        torch.cuda.empty_cache()
+        if rank == 0:
+            nonlinear_rec = nonlinear_measure(dev, max(args.steps, 20), 3)
+        if world > 1:
+            dist.barrier()
+
     if rank == 0:
         peaks = read_peaks()
         # dense INT8 tensor peak: no measured entry exists; use 2x the measured sustained bf16 cuBLAS rate (INT8 is nominally
@@ -332,12 +357,14 @@ def run_ours(args):
         if world == 1 and not args.no_cpu_baseline:
             from oracle import jetfire_oracle as O
             O.build_c_oracle()
-            cores = len(os.sched_getaffinity(0))
+            cores = O.set_threads(len(os.sched_getaffinity(0)))
             cpu_linear_sample(O, 128, 128, 1024)
             dt, ops = cpu_linear_sample(O, 512, 512, 8192)
             cpu = {"value": ops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
                    "sample": "fwd+dgrad+wgrad of a 512x512x8192 slice of the layer, CPU oracle (C, OpenMP), once"}
         ws_mb = (3 * M * K + 2 * M * N + 2 * M * N) / 2 ** 20
+        sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
+        traffic, traffic_src = forward_dram_traffic(M, N, K)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
                 "data": "synthetic",
@@ -354,17 +381,44 @@ def run_ours(args):
                              "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
                              "frac_of_nominal_4500": fwd_tops / 4500.0, "cublas_int_mm_tops": int_mm_tops,
                              "avg_launch_ms": fwd_ms,
-                             # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch, from the ncu capture
-                             # summarised in profiles/linear_8192_launches_and_traffic.md (only valid at that size)
-                             "traffic": NCU_FWD_DRAM_BYTES_8192 if (M, N, K) == (8192, 8192, 8192) else None,
+                             # the algorithm's own ceiling: every 128x128x32 block product needs 16384 int32->fp32 conversions
+                             # on a 64-lane-per-clock pipe = 256 SM clocks per K block, whatever the tensor core does
+                             "dequant_bound_tops": DEQUANT_BOUND_TOPS(sm_count, clocks),
+                             "frac_of_dequant_bound": fwd_tops / DEQUANT_BOUND_TOPS(sm_count, clocks),
+                             "traffic": traffic, "traffic_source": traffic_src,
                              "algorithmic_bytes": M * K + N * K + M * N + 2 * (M * K + N * K + M * N) // 1024},
-                "cpu_baseline": cpu, "gemm_error_flag": err}
+                "cpu_baseline": cpu, "gemm_error_flag": err, "gpt2": gpt2_rec, "nonlinear": nonlinear_rec}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-NCU_FWD_DRAM_BYTES_8192 = 331565824 + 57638144
+def DEQUANT_BOUND_TOPS(sm_count, clocks):
+    """Throughput at which the int32 -> fp32 conversions of the per-K-block rescale alone saturate their pipe: one 128x128x32
+    block product (2 * 128 * 128 * 32 ops) per 256 clocks per SM, at the SM clock sampled during the run."""
+    mhz = (clocks or {}).get("sm_mhz") or 1965.0
+    return sm_count * (2.0 * 128 * 128 * 32) / 256.0 * mhz * 1e6 / 1e12
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE forward launch at M = N = K = 8192 from an ncu capture, keyed by the
+# SHA-256 (first 16 hex digits) of the kernel sources it was taken with; a build from other sources reports null.
+NCU_FWD_DRAM_BYTES_8192 = {}
+
+
+def kernel_source_hash():
+    import hashlib
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "jetfire_int8training_b200", "csrc")
+    for f in ("gemm.cu", "gemm_kernel.cuh", "gemm_launch.inc", "ptx_sm100.cuh"):
+        h.update(open(os.path.join(csrc, f), "rb").read())
+    return h.hexdigest()[:16]
+
+
+def forward_dram_traffic(M, N, K):
+    key = kernel_source_hash()
+    if (M, N, K) == (8192, 8192, 8192) and key in NCU_FWD_DRAM_BYTES_8192:
+        return NCU_FWD_DRAM_BYTES_8192[key], f"ncu capture of one forward launch, kernel sources {key}"
+    return None, f"no ncu capture for kernel sources {key} at this size"
 
 
 def nonlinear_ops(M, N, copies, dev):
@@ -440,16 +494,23 @@ def run_nonlinear(args):
         ms = a.elapsed_time(b) / args.steps
         print(json.dumps({"op": args.op, "M": M, "N": N, "ms": ms, "GBps": bpe * M * N / (ms * 1e-3) / 1e9}), flush=True)
         return
+    print(json.dumps(nonlinear_measure(dev, args.steps, args.warmup)), flush=True)
+
+
+def nonlinear_measure(dev, steps, warmup):
+    """GB/s (algorithmic bytes) and fraction of the measured HBM bandwidth per nonlinear operator on [8192,768] and [8192,3072]."""
+    import torch
+    peaks = read_peaks()
     res = {}
     for (M, N) in ((8192, 768), (8192, 3072)):
         copies = max(4, int(300e6 // (M * N)) + 1)   # rotate through > 256 MB of int8 payload so L2 cannot serve the reads
         ops, keep = nonlinear_ops(M, N, copies, dev)
         for name, (fn, bpe) in ops.items():
-            for i in range(max(3, args.warmup)):
+            for i in range(max(3, warmup)):
                 assert fn(i) == 0, name
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            iters = max(args.steps, 2 * copies)
+            iters = max(steps, 2 * copies)
             a.record()
             for i in range(iters):
                 fn(i)
@@ -460,10 +521,10 @@ def run_nonlinear(args):
                                        "bytes_per_elt": bpe}
         del ops, keep
         torch.cuda.empty_cache()
-    print(json.dumps({"metric": "nonlinear operator GB/s (algorithmic bytes)", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm_gbs"],
-                      "peak_source": peaks["source"],
-                      "note": "C-ABI launches on preallocated buffers, inputs rotated through > 256 MB; CUDA events over the loop",
-                      "ops": res}), flush=True)
+    return {"metric": "nonlinear operator GB/s (algorithmic bytes)", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm_gbs"],
+            "peak_source": peaks["source"],
+            "note": "C-ABI launches on preallocated buffers, inputs rotated through > 256 MB; CUDA events over the loop",
+            "ops": res}
 
 
 def run_gpt2(args):
@@ -476,15 +537,28 @@ def run_gpt2(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    rec = gpt2_measure(args.model, args.micro_batch, args.steps, args.warmup, dev, rank, world, local, kernel_table=args.kernel_table)
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local, kernel_table=False):
+    """One GPT-2 INT8 data-parallel training measurement (the process group, if any, is already initialised).  Returns the
+    record on every rank (timing = max over ranks of the CUDA-event time)."""
+    import torch
+    import torch.distributed as dist
     from jetfire_int8training_b200 import rng
+    from jetfire_int8training_b200._lib import lib
     from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
-    if args.model == "xl":
+    if model_name == "xl":
         cfg, mb = GPTConfig(n_layer=48, n_head=25, n_embd=1600), 8
-    elif args.model == "tiny":
+    elif model_name == "tiny":
         cfg, mb = GPTConfig(n_layer=2, n_head=4, n_embd=256, block_size=256, vocab_size=4096), 4
     else:
         cfg, mb = GPTConfig(), 12
-    mb = args.micro_batch or mb
+    mb = micro_batch or mb
     torch.manual_seed(1337)
     rng.manual_seed(1337 + rank)
     model = QGPT(cfg).to(dev)
@@ -509,28 +583,28 @@ def run_gpt2(args):
         return loss
 
     losses = []
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         losses.append(float(step(*batch())))
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss = step(*batch())
     b.record(); torch.cuda.synchronize()
     ms = a.elapsed_time(b)
     if world > 1:
         tms = torch.tensor([ms], device=dev); dist.all_reduce(tms, op=dist.ReduceOp.MAX); ms = float(tms.item())
-    if rank == 0:
-        toks = world * mb * T * args.steps / (ms * 1e-3)
-        print(json.dumps({"metric": "GPT-2 INT8 train tokens/s", "value": toks, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-                          "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                          "dtype": "int8 linears/LN/GELU, bf16 attention + LM head, fp32 params", "data": "synthetic",
-                          "config": {"workload": f"GPT-2 {args.model} INT8 training step", "n_layer": cfg.n_layer, "n_embd": cfg.n_embd,
-                                     "micro_batch": mb, "seq_len": T, "params": model.num_params(), "parallelism": f"dp{world}"},
-                          "loss_first": losses[0], "loss_last": float(loss)}), flush=True)
-    if args.kernel_table and rank == 0:
+    err = lib().jf_igemm_error_flag()        # a bounded wait that expired inside a GEMM would make every number here void
+    toks = world * mb * T * steps / (ms * 1e-3)
+    rec = {"metric": "GPT-2 INT8 train tokens/s", "value": toks, "tokens_per_s": toks, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+           "warmup": max(3, warmup), "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+           "dtype": "int8 linears/LN/GELU, bf16 attention + LM head, fp32 params", "data": "synthetic",
+           "config": {"workload": f"GPT-2 {model_name} INT8 training step", "model": model_name, "n_layer": cfg.n_layer,
+                      "n_embd": cfg.n_embd, "micro_batch": mb, "seq_len": T, "params": model.num_params(), "parallelism": f"dp{world}"},
+           "loss_first": losses[0], "loss_last": float(loss), "gemm_error_flag": err}
+    if kernel_table and rank == 0:
         # device time per kernel over three more steps (torch.profiler, CUDA activity), largest first
         from torch.profiler import ProfilerActivity, profile
         with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
@@ -543,8 +617,8 @@ def run_gpt2(args):
         print(f"device time per step: {tot / 3:.1f} us", flush=True)
         for t, c, k in rows[:32]:
             print(f"{t / 3:10.1f} us/step {100 * t / tot:5.1f} %  x{c // 3:4d}  {k[:120]}", flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    del net, opt, model
+    return rec
 
 
 def run_gemm_sweep(args):
@@ -639,6 +713,7 @@ def main():
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the linear workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (kernel tuning runs)")
+    ap.add_argument("--no-extras", action="store_true", help="linear workload: skip the gpt2 and nonlinear records")
     ap.add_argument("--kernel-table", action="store_true", help="gpt2 workload: also print the device time per kernel")
     ap.add_argument("--op", default=None, help="nonlinear workload: run only this operator (profiling)")
     ap.add_argument("--rows", type=int, default=65536)

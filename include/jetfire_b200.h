@@ -110,7 +110,8 @@ int jf_int8_add_meanvar(const void* x1, int x1_dtype, const int8_t* q2, const vo
  * outside any stream capture.  The call itself never calls cudaMalloc/cudaFree or any allocating routine.
  * All calls on a device share the one array, which keeps the previous call's contents: nothing in it needs to start at
  * zero (every partial is rewritten before it is read), but two calls whose kernels overlap on the GPU (different streams
- * without ordering) race on it. */
+ * without ordering) race on it.  The array used is the one of the calling thread's CURRENT device (cudaGetDevice), which
+ * must be the device of `stream` and of every operand. */
 int jf_int8_add_meanvar_noalloc(const void* x1, int x1_dtype, const int8_t* q2, const void* s2, int64_t M, int64_t N,
                                 float* y1, int8_t* qy, void* sy, float* mean, float* rstd, void* stream);
 

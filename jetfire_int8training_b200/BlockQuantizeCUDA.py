@@ -17,7 +17,11 @@ def _stream():
 
 def igemm_output_int_quantize_bias_rowcol(X, Wt, bias, biasmax, SXt, SWt, M, N, K):
     """Forward Y = X W^T -> (int8 [M,N], fp16 [M/32,N/32]).  `bias` / `biasmax` must be zero (Jetfire always passes
-    zeros, Jetfire/Linear/linear_fwd.py:20-21); they are not read."""
+    zeros, Jetfire/Linear/linear_fwd.py:20-21): the reference kernel adds them before re-quantising
+    (igemm_BlockSquare32OutputIntQuantizeBiasRowCol.cu:341, 357), this one does not, so a non-zero tensor is refused.  The
+    check reads the two tensors back (one small device-to-host copy per call); `Linear.int8_linear_forward` does not pay it."""
+    if (bias is not None and bool(torch.count_nonzero(bias))) or (biasmax is not None and bool(torch.count_nonzero(biasmax))):
+        raise NotImplementedError("BlockQuantizeCUDA shim: a non-zero bias / biasmax is not implemented (Jetfire passes zeros)")
     dev = X.device
     O = torch.empty((M, N), dtype=torch.int8, device=dev)
     SO = torch.empty((M // 32, N // 32), dtype=torch.float16, device=dev)

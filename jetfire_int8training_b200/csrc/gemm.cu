@@ -1,5 +1,5 @@
 // Per-block (32x32) quantised INT8 GEMMs for sm_100a: forward Y = X W^T, input gradient dX = dY W and weight gradient
-// dW = dY^T X, all from one persistent, warp-specialised kernel.
+// dW = dY^T X, all from one persistent, warp-specialised kernel (gemm_kernel.cuh).
 //
 // Algorithm (fixed by the reference and its oracle): for every 32-wide K block p, in ascending order,
 //     I_p = A_blk x B_blk^T  (exact int32),      acc = fma(sa[i,p] * sb[j,p], float(I_p), acc)   (fp32)
@@ -7,25 +7,22 @@
 //
 // Mapping to the hardware
 //   * CTA tile 128 x 128, one CTA per SM, persistent over a static list of (tile, K-split) work items.
-//   * 384 threads = two consumer warpgroups + one producer warpgroup; setmaxnreg moves registers from the producer
-//     warpgroup (56 each) to the consumers (224 each) so the conversion/FMA stream has enough independent work in flight.
-//   * warp 8 (one lane): TMA producer.  A 128-byte-swizzled 128 x 128 B box per operand per stage = four K blocks;
-//     a 4-stage mbarrier ring (128 KB of shared memory).
-//   * warps 9-10 (one lane each): MMA issuers, alternating K blocks.  tcgen05.mma kind::i8 has K = 32 = one quantisation block, so every K block is ONE
-//     128x128x32 MMA with accumulation disabled, written to one of four 128-column TMEM accumulators (512 columns);
-//     tcgen05.commit signals the accumulator's "full" barrier and, after the last MMA of a stage, the stage's "empty" one.
-//   * warps 0-7: consumers.  Warp w reads TMEM lanes 32*(w%4).. (rows) and columns 64*(w/4).. of the current
-//     accumulator with tcgen05.ld (each thread: one row, 64 columns = two quantisation blocks), releases it, and does
-//     the int32 -> fp32 conversion and the scale FMA into 64 fp32 registers.  This CUDA-core work, not the tensor
-//     core, bounds the kernel.  Scales are fetched one fp16 per lane for 8 K blocks at a time and broadcast by shuffle.
+//   * 19 warps: 16 consumers, 1 TMA producer (one lane), 2 MMA issuers (one lane each).
+//   * producer: a 128-byte-swizzled 128 x 128 B box per operand per stage = four K blocks; a 4-stage mbarrier ring (128 KB).
+//   * issuers: tcgen05.mma kind::i8 has K = 32 = one quantisation block, so every K block is ONE 128x128x32 MMA with
+//     accumulation disabled.  Tensor memory (512 columns) holds two groups of two 128-column accumulators; the four K blocks
+//     of a stage form two pairs, pair g goes to group g and is issued by issuer g with one tcgen05.commit.
+//   * consumers: warp w reads TMEM lanes 32*(w%4).. (rows) and columns 32*(w/4).. of every accumulator with tcgen05.ld (a
+//     thread = one row of one quantisation block), converts int32 -> fp32 and does the scale FMA into 32 fp32 registers.  This
+//     CUDA-core work, not the tensor core, bounds the kernel.  Scale products are fetched one per lane for 8 K blocks at a
+//     time and broadcast by shuffle.
 //   * operands are consumed in place in either orientation: K-major (row-major [rows, K]) or MN-major (row-major
 //     [K, rows]) through the UMMA descriptor major bits, so no transposed copy of W, dY or X is ever materialised.
 //   * epilogue: a 32x32 block = 32 lanes x 32 thread-local values; absmax is a local max + one redux.sync.
-// Every mbarrier wait is bounded by a clock budget; on expiry the CTA raises an error flag, leaves its loops and
-// frees its tensor memory.
+// Every mbarrier wait is bounded by a clock budget; on expiry the CTA raises an error flag (read with jf_igemm_error_flag),
+// leaves its loops, waits (bounded) for its copies and MMAs in flight and frees its tensor memory.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -40,6 +37,7 @@ constexpr int STAGES = 4;
 constexpr int STAGE_BYTES = 128 * 128;          // one operand tile
 constexpr int TMEM_COLS = 512;
 constexpr size_t GEMM_SMEM = 2 * STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long DRAIN_BUDGET_CLOCKS = 20000000LL;   // ~10 ms: abort-path wait for copies / MMAs already in flight
 constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
 
 enum GemmMode : int {
@@ -63,15 +61,6 @@ struct GemmParams {
     int stochastic; const float* noise; uint64_t offset; PhiloxKeys keys;
 };
 
-#ifdef JF_TIMELINE
-// tuning builds only: clock stamps of CTA 0 (first events of the launch), read back with jf_debug_timeline
-__device__ long long g_timeline[8192];
-#define JF_STAMP(cond, idx) do { if ((cond) && blockIdx.x == 0) g_timeline[(idx)] = clock64(); } while (0)
-#define JF_TL_ON true
-#else
-#define JF_TL_ON false
-#define JF_STAMP(cond, idx) do { } while (0)
-#endif
 __device__ int g_gemm_error = 0;   // 0 = ok; otherwise the code of the first wait that expired
 
 // Wait for a barrier phase, giving up after WAIT_BUDGET_CLOCKS.  SUSPEND = true (producer and issuer warps): every try lets the
@@ -82,9 +71,6 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
-#ifdef JF_TIMELINE
-        if (blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_timeline[8000 + code]), 1ull);   // polls per wait site
-#endif
         if (SUSPEND ? ptx::mbar_try_wait_hint(bar, parity, 2000u) : ptx::mbar_try_wait(bar, parity)) return true;
         if ((it & (SUSPEND ? 31u : 255u)) == (SUSPEND ? 31u : 255u)) {
             if (*abort_flag) return false;
@@ -97,18 +83,20 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     }
 }
 
+// Abort path: wait for a barrier phase that operations already in flight will complete, without touching the abort state.
+__device__ __forceinline__ void drain_wait(uint64_t* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!ptx::mbar_try_wait_hint(bar, parity, 2000u))
+        if (clock64() - t0 > DRAIN_BUDGET_CLOCKS) break;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Consumer arithmetic.  acc is kept as packed pairs of fp32 so the scale FMA can use the two-wide fma.rn.f32x2.
-// int32 -> fp32 is exact for |I| <= 32*127^2 < 2^22 in either form:
-//   CONV_I2F  : cvt.rn.f32.s32 (conversion unit)
-//   CONV_MAGIC: bits(I + 0x4B400000) is the float 1.5*2^23 + I; subtracting 1.5*2^23 (exact) leaves float(I)
-//               (integer pipe + FMA pipe)
-//   CONV_MIXED: alternate pairs between the two, to spread the work over three pipes.
-//   CONV_SCALAR: cvt.rn.f32.s32 + scalar fma.rn.f32 (no packed pairs)
-// CONV_INT32 adds the raw integers (diagnostic int32 GEMM); the CONV_PROBE_* modes exist only to time the kernel's
-// data movement without its arithmetic and produce meaningless results.
+// int32 -> fp32 (cvt.rn.f32.s32) is exact: |I| <= 32*127^2 < 2^22.  (Building the float with an integer add of 0x4B400000 and
+// a subtraction of 1.5*2^23 instead, for all or for every other pair, measured slower: the add runs on the same pipe.)
+// CONV_INT32 adds the raw integers instead: the plain int32 GEMM behind jf_igemm_int32.
 // ---------------------------------------------------------------------------------------------------------
-enum ConvMode : int { CONV_I2F = 0, CONV_MAGIC = 1, CONV_SCALAR = 2, CONV_MIXED = 3, CONV_INT32 = 4, CONV_PROBE_NONE = 5 };
+enum ConvMode : int { CONV_I2F = 0, CONV_INT32 = 1 };
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
     uint64_t r;
@@ -116,75 +104,27 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
     return r;
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
 
-// The 32 fp32 accumulators of a consumer thread: packed pairs for the fma.rn.f32x2 forms, plain floats for CONV_SCALAR.
+// acc2[j] (16 packed pairs) += s * float(r[2j], r[2j+1]) for the 32 int32 values in r
 template <int CONV>
-struct Accum {
-    uint64_t v[16];
-    __device__ __forceinline__ void clear() {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0ull;
-    }
-    __device__ __forceinline__ void get(float (&ab)[32]) const {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) unpack2(v[j], ab[2 * j], ab[2 * j + 1]);
-    }
-};
-template <>
-struct Accum<CONV_SCALAR> {
-    float v[32];
-    __device__ __forceinline__ void clear() {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0.f;
-    }
-    __device__ __forceinline__ void get(float (&ab)[32]) const {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) ab[j] = v[j];
-    }
-};
-// CONV_SCALAR: acc[j] = fma(s, float(r[j]), acc[j]) with scalar instructions (no register pairing needed)
-__device__ __forceinline__ void scale_accumulate_scalar(float* acc, const uint32_t* r, float s) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) acc[j] = __fmaf_rn(s, __int2float_rn((int)r[j]), acc[j]);
-}
-
-// acc2[j] (NV/2 packed pairs) += s * float(r[2j], r[2j+1]) for the NV int32 values in r
-template <int CONV, int NV>
-__device__ __forceinline__ void scale_accumulate(uint64_t* acc2, const uint32_t* r, float s) {
+__device__ __forceinline__ void scale_accumulate(uint64_t (&acc2)[16], const uint32_t (&r)[32], float s) {
     if (CONV == CONV_INT32) {
 #pragma unroll
-        for (int j = 0; j < NV / 2; ++j) {
+        for (int j = 0; j < 16; ++j) {
             const uint32_t lo = (uint32_t)acc2[j] + r[2 * j], hi = (uint32_t)(acc2[j] >> 32) + r[2 * j + 1];
             acc2[j] = ((uint64_t)hi << 32) | lo;
         }
         return;
     }
-    if (CONV == CONV_PROBE_NONE) {
-        acc2[0] += ((uint64_t)r[1] << 32) | r[0];
-        return;
-    }
     const uint64_t s2 = pack2(s, s);
-    const uint64_t negc = pack2(-12582912.0f, -12582912.0f);
 #pragma unroll
-    for (int j = 0; j < NV / 2; ++j) {
-        const bool magic = (CONV == CONV_MAGIC) || (CONV == CONV_MIXED && (j & 1));
-        if (magic) {
-            const uint64_t x = add2(pack2(__int_as_float((int)r[2 * j] + 0x4B400000), __int_as_float((int)r[2 * j + 1] + 0x4B400000)), negc);
-            acc2[j] = fma2(s2, x, acc2[j]);
-        } else {
-            acc2[j] = fma2(s2, pack2(__int2float_rn((int)r[2 * j]), __int2float_rn((int)r[2 * j + 1])), acc2[j]);
-        }
-    }
+    for (int j = 0; j < 16; ++j)
+        acc2[j] = fma2(s2, pack2(__int2float_rn((int)r[2 * j]), __int2float_rn((int)r[2 * j + 1])), acc2[j]);
 }
 
 // Re-quantise / convert one 32x32 block held as 32 lanes x 32 values and store it.
@@ -492,11 +432,5 @@ int jf_igemm_error_flag(void) {
     if (v != 0) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
     return v;
 }
-
-#ifdef JF_TIMELINE
-int jf_debug_timeline(long long* host_out, int n) {
-    return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(long long) * (size_t)n) == cudaSuccess ? 0 : JF_ERR_LAUNCH;
-}
-#endif
 
 }  // extern "C"

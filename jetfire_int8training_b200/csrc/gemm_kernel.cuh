@@ -14,11 +14,11 @@
 // 32x32 quantisation block (32 fp32 accumulators in registers).  Every consumer warp has to walk through every K block, so the
 // length of one warp's chain per pair (barrier test, fences, two tcgen05.ld round trips, release, 2 x 48 arithmetic
 // instructions under four-way issue contention) is what bounds the kernel, not the tensor core (64 clocks per K block), the
-// issuers or the operand stream: with the arithmetic removed the same kernel runs 8192^3 in 1.13 ms, with it in 2.07 ms.
-// Measured alternatives that were slower: 8 consumer warps x 64 columns (2.73 ms), four single-accumulator slots with one
-// commit per K block (2.92 ms), 16-column chunks with the next chunk's load in flight (2.20 ms), reading both accumulators of a
-// pair before the arithmetic so the group is released at once (1.26 ms without arithmetic, but 64 raw registers spill at the 96
-// registers per thread that 19 warps allow: 3.6 - 6 ms).
+// issuers or the operand stream.
+//
+// Abort path.  Every wait is bounded; when one expires the CTA's roles leave their loops.  Before the CTA frees its tensor
+// memory the producer waits (bounded) for the bulk copies it has in flight and each issuer commits its outstanding MMAs to a
+// scratch barrier and waits (bounded) for it, so that nothing writes into shared or tensor memory of an exited CTA.
 #pragma once
 
 // Tile rasterisation: tiles are numbered in groups of RASTER_GM tile-rows, M-fastest inside a group, so the ~148 tiles that
@@ -56,7 +56,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint64_t* empty_bar = bars + STAGES;                  // [STAGES]   consumers (int32 mode: MMA) -> TMA
     uint64_t* grp_full = bars + 2 * STAGES;               // [NUM_GRP]  MMA -> consumers
     uint64_t* grp_empty = bars + 2 * STAGES + NUM_GRP;    // [NUM_GRP]  consumers -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NUM_GRP);
+    uint64_t* drain_bar = bars + 2 * STAGES + 2 * NUM_GRP;  // [NUM_ISSUERS]  abort path only: outstanding MMAs of an issuer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NUM_GRP + NUM_ISSUERS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -64,6 +65,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
         for (int g = 0; g < NUM_GRP; ++g) { ptx::mbar_init(&grp_full[g], 1); ptx::mbar_init(&grp_empty[g], EPI_WARPS); }
+        for (int g = 0; g < NUM_ISSUERS; ++g) ptx::mbar_init(&drain_bar[g], 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -104,6 +106,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (B_MN) ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], (int32_t)(tn * BN), k_off);
                     else      ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], k_off, (int32_t)(tn * BN));
                 }
+            }
+            if (*abort_flag) {
+                // abort: the copies of the last (up to STAGES) armed stages may still be landing in this CTA's shared memory
+                for (uint32_t j = it > STAGES ? it - STAGES : 0u; j < it; ++j) drain_wait(&full_bar[j % STAGES], (j / STAGES) & 1u);
             }
         }
     } else if (warp >= WARP_MMA) {
@@ -155,6 +161,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     }
                 }
             }
+            if (*abort_flag) {
+                // abort: wait until every MMA this thread has issued has completed (they read shared and write tensor memory)
+                ptx::umma_commit(&drain_bar[w]);
+                drain_wait(&drain_bar[w], 0u);
+            }
         }
     } else {
         // ------------------------------------------------------------------ consumers
@@ -176,12 +187,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int colblk = tn32 * (BN / QB) + cgrp;
             const bool blk_ok = rowblk < (int)(p.M / QB) && colblk < (int)(p.N / QB);   // warp-uniform
 
-            Accum<CONV> acc_regs;   // the thread's 32 fp32 accumulators
-            acc_regs.clear();
-            auto accumulate = [&](const uint32_t (&raw)[32], float sc) {
-                if constexpr (CONV == CONV_SCALAR) scale_accumulate_scalar(acc_regs.v, raw, sc);
-                else scale_accumulate<CONV, 32>(acc_regs.v, raw, sc);
-            };
+            uint64_t acc2[16];   // the thread's 32 fp32 accumulators as packed pairs
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
+            auto accumulate = [&](const uint32_t (&raw)[32], float sc) { scale_accumulate<CONV>(acc2, raw, sc); };
 
             // lanes 0-7 hold the scale products sa*sb of 8 consecutive K blocks
             const __half* sa_ptr = p.sa + (int64_t)rowblk * p.sa_sm + (int64_t)(kb0 + (lane & 7)) * p.sa_sk;
@@ -207,11 +216,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             // K block is converted and accumulated before the second one is read, and only then can the group be released.
             // Reading both first and releasing at once would shorten the hand-over (measured without arithmetic: 1.26 ms
             // instead of 1.43 ms at 8192^3) but needs 64 raw registers, and the spills cost far more than that.
-            auto do_pair = [&](const uint32_t g, const bool two, const float s0, const float s1, const bool stage_end,
-                               [[maybe_unused]] const int t) -> bool {
+            auto do_pair = [&](const uint32_t g, const bool two, const float s0, const float s1, const bool stage_end) -> bool {
                 const uint32_t acc = lane_base + g * GRP_COLS;
-                [[maybe_unused]] const bool tl = JF_TL_ON && blockIdx.x == 0 && threadIdx.x == 0 && item == blockIdx.x && t < 200;
-                JF_STAMP(tl, t * 8 + 0);
                 {
                     const uint32_t uses = INT32ACC ? use0 / NUM_GRP : (g ? use1 : use0);
                     const bool got = bounded_wait(&grp_full[g], uses & 1u, abort_flag, 4);
@@ -219,14 +225,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (g && !INT32ACC) ++use1; else ++use0;
                     ptx::tc_fence_after();
                 }
-                JF_STAMP(tl, t * 8 + 1);
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(acc, r);
                 ptx::tmem_wait_ld_regs(r);
-                JF_STAMP(tl, t * 8 + 2);
                 if (two) {
                     accumulate(r, s0);
-                    JF_STAMP(tl, t * 8 + 3);
                     ptx::tmem_ld_32x32b_x32(acc + BN, r);
                     ptx::tmem_wait_ld_regs(r);
                 }
@@ -240,9 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (warp == 0 && lane == 0) ptx::mbar_arrive(&empty_bar[sit % STAGES]);
                     ++sit;
                 }
-                JF_STAMP(tl, t * 8 + 4);
                 accumulate(r, two ? s1 : s0);
-                JF_STAMP(tl, t * 8 + 5);
                 return true;
             };
 
@@ -256,7 +257,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     for (int pp = 0; pp < 4; ++pp) {
                         if (!ok) break;
                         ok = do_pair((uint32_t)(pp & 1), true, __shfl_sync(0xffffffffu, sc_cur, 2 * pp),
-                                     __shfl_sync(0xffffffffu, sc_cur, 2 * pp + 1), (pp & 1) == 1, t + 2 * pp);
+                                     __shfl_sync(0xffffffffu, sc_cur, 2 * pp + 1), (pp & 1) == 1);
                     }
                 }
             }
@@ -270,14 +271,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
                 const float s0 = __shfl_sync(0xffffffffu, sc_cur, pi);
                 const float s1 = __shfl_sync(0xffffffffu, sc_cur, pi + 1);
-                ok = do_pair(g, t + 1 < nloop, s0, s1, g == 1 || t + 2 >= nloop, t);
+                ok = do_pair(g, t + 1 < nloop, s0, s1, g == 1 || t + 2 >= nloop);
             }
             if (!ok) break;
 
             // ---------------------------------------------------------------- tile epilogue
             if (!blk_ok) continue;
             float ab[32];
-            acc_regs.get(ab);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) unpack2(acc2[j], ab[2 * j], ab[2 * j + 1]);
             store_block(p, ab, (int64_t)tm32 * BM + quad * 32 + lane, (int64_t)colblk * QB, rowblk, colblk, split32, lane);
         }
     }

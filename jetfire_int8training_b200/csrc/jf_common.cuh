@@ -28,22 +28,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline bool mult32(int64_t v) { return v > 0 && (v % 32) == 0; }
 
 // ---------------------------------------------------------------------------------------------------------
-// Philox4x32-10 (Random123).  One call yields the four words of the group g = element_index / 4.
+// Philox4x32-10 (Random123) and the stochastic-rounding noise
 // ---------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
-#pragma unroll
-    for (int r = 0; r < 10; ++r) {
-        if (r > 0) {
-            k.x += 0x9E3779B9u;
-            k.y += 0xBB67AE85u;
-        }
-        const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
-        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
-        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
-    }
-    return c;
-}
-
 // Noise mapping.  One Philox call (four 32-bit words) serves the 8 consecutive elements of group g = e / 8; element e uses the
 // 16-bit half (e & 1) of word (e >> 1) & 3:  noise = h * 2^-16 - 0.5, a multiple of 2^-16 in [-0.5, 0.5) like the reference's
 // uniform_(-0.5, 0.5).  Built without an int->float conversion: the half is placed in the low mantissa bits of 2^23, and one
@@ -109,31 +95,7 @@ __device__ __forceinline__ Divisor make_divisor(float b) {
     d.fast = (ab >= 8.673617379884035e-19f) && (ab <= 1.152921504606847e18f);
     return d;
 }
-__device__ __forceinline__ float div_exact(float a, const Divisor& d) {
-    if (d.fast) {
-        const float q0 = __fmul_rn(a, d.inv);
-        const float r = __fmaf_rn(-d.b, q0, a);
-        return __fmaf_rn(r, d.inv, q0);
-    }
-    return __fdiv_rn(a, d.b);
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// Rounding to int8
-// ---------------------------------------------------------------------------------------------------------
-// Stochastic-rounding pre-step of the reference: sign(v) * clamp(|v| + noise, -128, 127).
-__device__ __forceinline__ float sr_prestep(float v, float noise) {
-    const float mag = fminf(fmaxf(__fadd_rn(fabsf(v), noise), -128.f), 127.f);
-    return (__float_as_uint(v) >> 31) ? -mag : mag;
-}
-// Round-half-even to an integer and keep the low byte (llrint followed by a narrowing cast); |v| < 2^22.
-__device__ __forceinline__ uint32_t rne_byte(float v) { return __float_as_uint(__fadd_rn(v, 12582912.0f)) & 0xFFu; }
-// Truncation toward zero, low byte (a plain float -> int8 cast).
-__device__ __forceinline__ uint32_t trunc_byte(float v) { return ((uint32_t)__float2int_rz(v)) & 0xFFu; }
-
-__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
-    return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-}
+// use: q0 = a * d.inv;  q = fma(fma(-d.b, q0, a), d.inv, q0)   (d.fast)      or      q = a / d.b   (otherwise)
 
 // fp16 product of an int8 payload value and its fp16 scale, as the reference's "int8 * fp16" does
 // (the int8 is converted to fp16 exactly, the product is rounded to fp16 once).  q*s is exact in fp32.
@@ -146,19 +108,6 @@ __device__ __forceinline__ int sbyte(uint32_t w, int i) { return (int)(int8_t)(w
 __device__ __forceinline__ float byte_to_float(uint32_t wx, int k) {
     const uint32_t sel = k == 0 ? 0x7440u : k == 1 ? 0x7441u : k == 2 ? 0x7442u : 0x7443u;   // {byte k, 0x00, 0x00, 0x4B}
     return __fadd_rn(__uint_as_float(__byte_perm(wx, 0x4B000000u, sel)), -8388736.0f);
-}
-
-// 1 - erf(|z|) * ... building block of the GELU kernels: for u = |x| / sqrt(2),
-//   erfc(u) ~= t * (a1 + t*(a2 + t*(a3 + t*(a4 + t*a5)))) * exp(-u^2),  t = 1 / (1 + p*u)        (Abramowitz-Stegun 7.1.26,
-// absolute error <= 1.5e-7).  Returns the polynomial factor; the caller multiplies by exp(-x^2/2), which the backward kernel
-// needs anyway for the density term.
-__device__ __forceinline__ float erfc_poly(float u) {
-    const float t = __frcp_rn(__fmaf_rn(0.3275911f, u, 1.0f));
-    float q = __fmaf_rn(1.061405429f, t, -1.453152027f);
-    q = __fmaf_rn(q, t, 1.421413741f);
-    q = __fmaf_rn(q, t, -0.284496736f);
-    q = __fmaf_rn(q, t, 0.254829592f);
-    return __fmul_rn(q, t);
 }
 
 // dtype-generic 16-element row chunk loads -> fp32

@@ -1,20 +1,22 @@
 // INT8-in / INT8-out nonlinear operators of the Jetfire data flow, written for sm_100a.
 //
 // All kernels are streaming kernels built on one work decomposition:
-//   * a warp owns a tile of 32 rows x TW columns (TW = 64 or 128, i.e. two or four 32x32 quantisation blocks);
+//   * a warp owns a tile of 32 rows x TW columns (TW = 32 or 64, i.e. one or two 32x32 quantisation blocks);
 //   * a lane owns a 16-column chunk: with LPR = TW/16 lanes per row, lane = (rg, cc), rg = lane / LPR (row group),
 //     cc = lane % LPR (chunk); in pass i (0 .. LPR-1) the lane touches row i*(32/LPR) + rg, columns [16*cc, 16*cc + 16):
-//     one 16-byte access per int8 row chunk, every access of a warp covers whole 64/128-byte row segments, and all loads of a
+//     one 16-byte access per int8 row chunk, every access of a warp covers whole 32/64-byte row segments, and all loads of a
 //     tile are issued before the first use;
 //   * a quantisation block is held by lanes {cc in {2b, 2b+1}} x all rg; its absmax is a thread-local max plus __shfl_xor
 //     steps over lane bit 0 and the rg bits;
 //   * the re-quantising division is an exact IEEE quotient computed with a shared correctly-rounded reciprocal (fast path
 //     chosen once per warp), rounding is an add of 1.5*2^23, bytes are gathered with prmt;
 //   * int8 -> fp32 avoids the conversion unit (prmt into the mantissa of 2^23, one subtract).
-// The narrow tile (64 values per thread) keeps the register count low enough for 3 CTAs of 8 warps per SM, which is what keeps
-// enough loads in flight to approach HBM bandwidth; kernels that need a 128-column slab (LayerNorm backward, residual add with
-// row statistics) use the wide tile.
-#include <cstdlib>
+// Tile widths: 32 columns (at most 80 registers, three 8-warp CTAs per SM) for the kernels with arithmetic per element --
+// quantize, GELU forward / backward, LayerNorm forward, the residual adds -- which is what keeps enough loads in flight;
+// 64 columns for the pure data movers (dequantize, transpose, quantize with the transposed copy).  LayerNorm backward and the
+// residual add with row statistics work on the reference's 128-column slab: two warps of 64 columns, resp. one warp walking
+// four 32-column tiles.
+#include <mutex>
 #include <type_traits>
 
 #include "jf_common.cuh"
@@ -440,50 +442,45 @@ transpose_kernel(const int8_t* __restrict__ x, int64_t M, int64_t N, int8_t* __r
 }
 
 // =========================================================================================================
-// GELU.  Phi(x) = 0.5 * (1 + erf(x / sqrt(2))) is evaluated as 1 - 0.5*erfc(u) (x >= 0) or 0.5*erfc(u) (x < 0), u = |x|/sqrt(2),
-// erfc(u) = P(1/(1+p*u)) * exp(-x^2/2)  (Abramowitz-Stegun 7.1.26, absolute error <= 1.5e-7: orders of magnitude below one
-// quantisation step of the output, and the exponential is shared with the density term of the backward pass).
+// GELU.  Both kernels go through per-block lookup tables: inside one 32x32 quantisation block the input is q * s with a single
+// scale s, so it takes at most 256 different values, and so does any function of it.  The transcendental functions are
+// evaluated CORRECTLY ROUNDED (in fp64, rounded once to fp32), which is what makes the payloads bit-identical to the CPU
+// restatement of the reference on every input; the tables make that affordable (at most 256 evaluations per 1024 elements).
 // =========================================================================================================
-__device__ __forceinline__ float rcp_approx(float x) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-    return r;
-}
-// returns Phi(x); *ex receives exp(-x^2/2)
-__device__ __forceinline__ float gelu_cdf(float x, float* ex) {
-    const float u = __fmul_rn(fabsf(x), 0.70710678118654752f);
-    const float tt = rcp_approx(__fmaf_rn(0.3275911f, u, 1.0f));
-    float pq = __fmaf_rn(1.061405429f, tt, -1.453152027f);
-    pq = __fmaf_rn(pq, tt, 1.421413741f);
-    pq = __fmaf_rn(pq, tt, -0.284496736f);
-    pq = __fmaf_rn(pq, tt, 0.254829592f);
-    const float e = __expf(__fmul_rn(__fmul_rn(x, x), -0.5f));
-    *ex = e;
-    const float half_erfc = __fmul_rn(__fmul_rn(pq, tt), __fmul_rn(0.5f, e));
-    return x < 0.f ? half_erfc : __fsub_rn(1.0f, half_erfc);
+constexpr float SQRT2_F = 1.41421353816986083984375f;      // sqrt(2) rounded to fp32 (the reference divides by this value)
+constexpr float SQRT2PI_F = 2.50662827491760253906250f;    // fp32 sqrt of fp32(2*pi)
+
+// Forward: the input of the function is the fp16 product x = fp16(q * s), so y(x) = x * Phi(x) has only 65536 possible arguments.
+// They are tabulated once per device (256 KB, stays in L2): entry = bit pattern of x.
+__device__ float g_gelu_fwd_table[65536];
+
+__global__ void gelu_fwd_table_kernel() {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 65536u) return;
+    const float x = __half2float(__ushort_as_half((unsigned short)i));
+    const float u = __fdiv_rn(x, SQRT2_F);
+    const float er = (float)erf((double)u);
+    const float cdf = __fmul_rn(__fadd_rn(1.0f, er), 0.5f);   // (1 + erf) / 2: the halving is exact
+    g_gelu_fwd_table[i] = __fmul_rn(cdf, x);
 }
 
-// Both GELU kernels go through a per-block lookup table: inside one 32x32 quantisation block the input is q * s with a single
-// scale s, so it takes at most 256 different values, and so does any function of it.  Per tile the warp evaluates the function
-// once for every payload value of each of its blocks (256 * TW/32 evaluations instead of 32 * TW) into shared memory, and every
-// element costs one shift + mask + shared-memory load.  The result is bit-identical to evaluating the function per element.
-template <int TW, class F>
-__device__ __forceinline__ void build_block_lut(float* lut /* [TW/32][256] of this warp */, float my_scale, const Tile& t, F&& f) {
-    constexpr int BLOCKS = TW / 32, PER_LANE = BLOCKS * 256 / 32;
-    __syncwarp();   // the previous tile's lookups are done
-    const int e0 = t.lane * PER_LANE;            // entries e0 .. e0 + PER_LANE - 1, all inside one block's table
-    const int b = e0 >> 8;
-    // the scale of block b is held by the lanes whose chunk lies in that block: take it from row group 0, chunk 2b
-    const float sc = __shfl_sync(0xffffffffu, my_scale, 2 * b);
-    float out[PER_LANE];
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) out[j] = f((float)(int8_t)(uint8_t)((e0 + j) & 255), sc);
-#pragma unroll
-    for (int j = 0; j < PER_LANE; j += 4)
-        *reinterpret_cast<float4*>(lut + e0 + j) = make_float4(out[j], out[j + 1], out[j + 2], out[j + 3]);
-    __syncwarp();
+// address of entry `byte k of w` of a 256-byte table that starts at the 256-byte-aligned shared address `base`
+template <int K>
+__device__ __forceinline__ uint32_t byte_entry_addr(uint32_t w, uint32_t base) {
+    return __byte_perm(w, base, 0x7650 + K);
 }
-// the 16 table values of one row chunk (payload bytes in r) from this lane's block table
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// the four table bytes selected by the four payload bytes of w
+__device__ __forceinline__ uint32_t translate4(uint32_t w, uint32_t base) {
+    const uint32_t b0 = lds_u8(byte_entry_addr<0>(w, base)), b1 = lds_u8(byte_entry_addr<1>(w, base));
+    const uint32_t b2 = lds_u8(byte_entry_addr<2>(w, base)), b3 = lds_u8(byte_entry_addr<3>(w, base));
+    return gather_bytes(b0, b1, b2, b3);
+}
+// the 16 fp32 table values of one row chunk (payload bytes in r) from a 256-entry fp32 table
 __device__ __forceinline__ void lookup16(const float* lut_b, const int4& r, float (&f)[16]) {
     const uint32_t w[4] = {(uint32_t)r.x, (uint32_t)r.y, (uint32_t)r.z, (uint32_t)r.w};
     const char* base = reinterpret_cast<const char*>(lut_b);
@@ -496,15 +493,32 @@ __device__ __forceinline__ void lookup16(const float* lut_b, const int4& r, floa
         }
 }
 
-// forward: x = fp16(q*s); y = x * Phi(x); block quantise with amax + 5e-5
-template <int TW>
-__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : (TW == 64 ? 2 : 1))
+// forward: x = fp16(q*s); y = x * Phi(x); block quantise with amax + 5e-5.
+// Per 32x32 block (= one warp tile) the kernel builds the table "input payload -> OUTPUT payload" (256 bytes) and translates
+// every element through it.  Exactness without evaluating erf exactly 256 times per block:
+//   (1) block absmax: y is non-decreasing for x > 0 and |y| < 0.17 for x < 0, so when y(largest positive payload) >= 0.17
+//       that value IS the absmax -- one SIMD byte max per four elements and ONE lookup of the exact device table;
+//   (2) table entries: lane l evaluates the magnitudes |q| = 4l+1 .. 4l+4 with erff (<= 2 ulp) and derives the entries of +q
+//       and -q.  The approximate quotient differs from the exact one by less than `margin` (bound below); when it lies further
+//       than that from a rounding boundary its rounding IS the exact payload, otherwise (a few entries in 10^4) the entry is
+//       recomputed from the exact device table with the exact division;
+//   (3) a block of small inputs (absmax below 0.17, rare) takes the exact table for everything.
+// Error bound of (2): |erff - erf| <= 2 ulp <= 1.2e-7, the argument x*0.70710678f differs from the reference's x/sqrt(2) by
+// <= 1.5 ulp (<= 0.9e-7 in erf), the exact erf is itself rounded (3e-8); (1 +- erf)/2 and the product with x round once more
+// in both chains: |y~ - y| <= 3e-7 |x|.  The test uses twice that, plus 4e-5 for the roundings of the quotient itself.
+__device__ __forceinline__ float gelu_table(const __half x16) { return __ldg(&g_gelu_fwd_table[__half_as_ushort(x16)]); }
+
+__global__ void __launch_bounds__(THREADS, 3)
 gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, int64_t M, int64_t N, int8_t* __restrict__ qy,
                 __half* __restrict__ sy) {
-    constexpr int NP = Geo<TW>::NP;
+    constexpr int TW = 32, NP = Geo<TW>::NP;
     using Raw = RawQ<NP>;
-    __shared__ __align__(16) float lut_all[WARPS][TW / 32][256];
-    float* lut = &lut_all[threadIdx.x >> 5][0][0];
+    __shared__ __align__(16) float ytab_all[WARPS][256];          // slow path only
+    __shared__ __align__(256) uint8_t btab_all[WARPS][256];
+    const int warp = threadIdx.x >> 5;
+    float* ytab = ytab_all[warp];
+    uint8_t* btab_g = btab_all[warp];
+    const uint32_t btab = (uint32_t)__cvta_generic_to_shared(btab_g);
     for_each_tile<TW, Raw, true>(
         M, N,
         [&](const Tile& t, Raw& r) {
@@ -512,34 +526,104 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
             r.sc = load_scale16(sx, t, N);
         },
         [&](const Tile& t, Raw& r) {
-            build_block_lut<TW>(lut, __half2float(r.sc), t, [](float q, float sc) {
-                const float x = __half2float(__hmul_rn(__float2half_rn(q), __float2half_rn(sc)));   // the reference's fp16 product
-                float e;
-                return __fmul_rn(gelu_cdf(x, &e), x);
-            });
-            const float* lut_b = lut + (t.cc >> 1) * 256;
-            float v[NP][16];
+            const int lane = t.lane;
+            // largest payload of the block
+            uint32_t m4 = 0x80808080u;   // four int8 -128
 #pragma unroll
-            for (int i = 0; i < NP; ++i) lookup16(lut_b, r.d[i], v[i]);
-            const float amax = __fadd_rn(block_max<TW>(absmax_tile<NP>(v)), 5e-5f);
-            const float scale32 = __fdiv_rn(amax, 127.0f);
-            SrCfg sr{};
-            emit_quantized<TW, false, false, false>([&](int i, float (&a)[16]) {
+            for (int i = 0; i < NP; ++i) {
+                m4 = __vmaxs4(m4, (uint32_t)r.d[i].x); m4 = __vmaxs4(m4, (uint32_t)r.d[i].y);
+                m4 = __vmaxs4(m4, (uint32_t)r.d[i].z); m4 = __vmaxs4(m4, (uint32_t)r.d[i].w);
+            }
+            m4 = __vmaxs4(m4, m4 >> 16);
+            m4 = __vmaxs4(m4, m4 >> 8);
+            const int qmax = __reduce_max_sync(0xffffffffu, (int)(int8_t)(m4 & 0xFFu));
+            float amax = qmax > 0 ? gelu_table(__hmul_rn(__int2half_rn(qmax), r.sc)) : 0.f;
+            const bool fast_tile = amax >= 0.17f;     // warp-uniform
+            __syncwarp();                             // the previous tile's translation is done
+            if (!fast_tile) {
+                // (3) every table entry from the exact device table, absmax over the elements
+                float y[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) a[j] = v[i][j];
-            }, scale32, t, M, N, qy, sy, sr, nullptr, nullptr);
+                for (int j = 0; j < 8; ++j) y[j] = gelu_table(__hmul_rn(__int2half_rn((int)(int8_t)(uint8_t)(8 * lane + j)), r.sc));
+                *reinterpret_cast<float4*>(ytab + 8 * lane) = make_float4(y[0], y[1], y[2], y[3]);
+                *reinterpret_cast<float4*>(ytab + 8 * lane + 4) = make_float4(y[4], y[5], y[6], y[7]);
+                __syncwarp();
+                float m = 0.f;
+#pragma unroll
+                for (int i = 0; i < NP; ++i) {
+                    float f[16];
+                    lookup16(ytab, r.d[i], f);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(f[j]));
+                }
+                amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
+                const float scale32 = __fdiv_rn(__fadd_rn(amax, 5e-5f), 127.0f);
+                uint32_t b[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(__fadd_rn(__fdiv_rn(y[j], scale32), 12582912.0f));
+                *reinterpret_cast<uint2*>(btab_g + 8 * lane) = make_uint2(gather_bytes(b[0], b[1], b[2], b[3]), gather_bytes(b[4], b[5], b[6], b[7]));
+            }
+            const float scale32 = __fdiv_rn(__fadd_rn(amax, 5e-5f), 127.0f);
+            if (fast_tile) {
+                // (2) scale32 >= 0.17/127: the exact quotient is the Markstein sequence with the correctly rounded reciprocal
+                const float inv = __frcp_rn(scale32);
+                uint32_t bp[4], bn[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int a = 4 * lane + 1 + j;                                   // |q| = 1 .. 128
+                    const __half x16 = __hmul_rn(__int2half_rn(a), r.sc);             // the reference's fp16 product (odd in q)
+                    const float x = __half2float(x16);
+                    const float er = erff(__fmul_rn(x, 0.70710678118654752f));
+                    const float hx = __fmul_rn(0.5f, x);
+                    const float yp = __fmul_rn(__fadd_rn(1.0f, er), hx), yn = -__fmul_rn(__fsub_rn(1.0f, er), hx);
+                    const float margin = __fmaf_rn(__fmul_rn(6e-7f, x), inv, 4e-5f);
+                    float vp = __fmul_rn(yp, inv), vn = __fmul_rn(yn, inv);
+                    float rp = __fadd_rn(vp, 12582912.0f), rn = __fadd_rn(vn, 12582912.0f);
+                    // distance of v to the integer it rounds to; beyond 0.5 - margin the exact value may round the other way.
+                    // (negated comparison: a NaN from an overflowing input takes the exact path as well)
+                    if (!(fabsf(__fsub_rn(vp, __fsub_rn(rp, 12582912.0f))) < __fsub_rn(0.5f, margin))) {
+                        const float y = gelu_table(x16), q0 = __fmul_rn(y, inv);
+                        rp = __fadd_rn(__fmaf_rn(__fmaf_rn(-scale32, q0, y), inv, q0), 12582912.0f);
+                    }
+                    if (!(fabsf(__fsub_rn(vn, __fsub_rn(rn, 12582912.0f))) < __fsub_rn(0.5f, margin))) {
+                        const float y = gelu_table(__hneg(x16)), q0 = __fmul_rn(y, inv);
+                        rn = __fadd_rn(__fmaf_rn(__fmaf_rn(-scale32, q0, y), inv, q0), 12582912.0f);
+                    }
+                    bp[j] = __float_as_uint(rp); bn[j] = __float_as_uint(rn);
+                }
+                // entries 4l+1 .. 4l+4 (the last lane's +128 does not exist: that byte is -128's) and 252-4l .. 255-4l
+                if (lane < 31) {
+                    btab_g[4 * lane + 1] = (uint8_t)bp[0]; btab_g[4 * lane + 2] = (uint8_t)bp[1];
+                    btab_g[4 * lane + 3] = (uint8_t)bp[2]; btab_g[4 * lane + 4] = (uint8_t)bp[3];
+                } else {
+                    btab_g[125] = (uint8_t)bp[0]; btab_g[126] = (uint8_t)bp[1]; btab_g[127] = (uint8_t)bp[2];
+                }
+                *reinterpret_cast<uint32_t*>(btab_g + 252 - 4 * lane) = gather_bytes(bn[3], bn[2], bn[1], bn[0]);
+                if (lane == 0) btab_g[0] = 0;          // y(0) = 0
+            }
+            __syncwarp();
+            // translate and store
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const int4 o = make_int4((int)translate4((uint32_t)r.d[i].x, btab), (int)translate4((uint32_t)r.d[i].y, btab),
+                                         (int)translate4((uint32_t)r.d[i].z, btab), (int)translate4((uint32_t)r.d[i].w, btab));
+                *reinterpret_cast<int4*>(qy + row_of<TW>(t, i) * N + t.col) = o;
+            }
+            if (lane == 0) sy[t.tm * (N / QB) + (t.col >> 5)] = __float2half_rn(scale32);
         });
 }
 
-// backward: x = q*s, g = qg*sg in fp32; d = (Phi(x) + x*phi(x)) * g; block quantise (+SR)
-template <int TW, bool SR>
-__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : (TW == 64 ? 2 : 1))
+// backward: x = q*s, g = qg*sg in fp32; d = (Phi(x) + x*phi(x)) * g; block quantise (+SR).
+// The table holds Phi(x) + x*phi(x) for the 256 payload values of the block.  erf and exp are odd / even in x, so one fp64
+// evaluation of each serves +q and -q: 128 evaluations per block, four per lane.
+template <bool SR>
+__global__ void __launch_bounds__(THREADS, 3)
 gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
                 const __half* __restrict__ sg, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd, SrCfg sr) {
-    constexpr int NP = Geo<TW>::NP;
+    constexpr int TW = 32, NP = Geo<TW>::NP;
     using Raw = RawQ2<NP>;
-    __shared__ __align__(16) float lut_all[WARPS][TW / 32][256];
-    float* lut = &lut_all[threadIdx.x >> 5][0][0];
+    __shared__ __align__(16) float lut_all[WARPS][256];
+    float* lut = lut_all[threadIdx.x >> 5];
     for_each_tile<TW, Raw, true>(
         M, N,
         [&](const Tile& t, Raw& r) {
@@ -549,20 +633,26 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
             r.sb = load_scale16(sg, t, N);
         },
         [&](const Tile& t, Raw& r) {
-            build_block_lut<TW>(lut, __half2float(r.sa), t, [](float q, float sc) {
-                const float x = __fmul_rn(q, sc);
-                float e;
-                const float cdf = gelu_cdf(x, &e);
-                const float pdf = __fmul_rn(__fmul_rn(x, 0.3989422804014327f), e);
-                return __fadd_rn(cdf, pdf);
-            });
-            const float* lut_b = lut + (t.cc >> 1) * 256;
+            const float scx = __half2float(r.sa);
+            __syncwarp();   // the previous tile's lookups are done
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int a = 4 * t.lane + 1 + j;                        // |q| = 1 .. 128
+                const float x = __fmul_rn((float)a, scx);                // exact
+                const float er = (float)erf((double)__fdiv_rn(x, SQRT2_F));
+                const float e = (float)exp((double)__fmul_rn(__fmul_rn(x, x), -0.5f));
+                const float ex = __fmul_rn(__fdiv_rn(x, SQRT2PI_F), e);
+                if (a < 128) lut[a] = __fadd_rn(__fmul_rn(0.5f, __fadd_rn(1.0f, er)), ex);
+                lut[256 - a] = __fsub_rn(__fmul_rn(0.5f, __fsub_rn(1.0f, er)), ex);
+            }
+            if (t.lane == 0) lut[0] = 0.5f;
+            __syncwarp();
             const float scg = __half2float(r.sb);
             float v[NP][16];
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
                 float fd[16], fg[16];
-                lookup16(lut_b, r.a[i], fd);
+                lookup16(lut, r.a[i], fd);
                 unpack16(r.b[i], fg);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(fd[j], __fmul_rn(fg[j], scg));
@@ -579,7 +669,7 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
 // LayerNorm forward: y = ((fp16(q*s) - mean) * rstd) * gamma; statistics are inputs
 // =========================================================================================================
 template <int TW>
-__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : (TW == 64 ? 2 : 1))
+__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : 2)
 ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const float* __restrict__ gamma,
               const float* __restrict__ mean, const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qy,
               __half* __restrict__ sy) {
@@ -628,7 +718,7 @@ ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
 // the warps, through shared memory and a 64-thread named barrier per row pass.  The sum order is the one of a single warp over
 // 8 lanes: ((l0+l1)+(l2+l3)) + ((l4+l5)+(l6+l7)).
 template <bool SR, int TW = 64>
-__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : 2)
+__global__ void __launch_bounds__(THREADS, 2)
 ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
               const __half* __restrict__ sg, const float* __restrict__ gamma, const float* __restrict__ mean,
               const float* __restrict__ rstd, int64_t M, int64_t N, int8_t* __restrict__ qd, __half* __restrict__ sd,
@@ -748,7 +838,7 @@ __global__ void __launch_bounds__(256) ln_bwd_dw_kernel(const float* __restrict_
 // registers and one CTA per SM and was latency-bound).  With MEANVAR a warp walks the 128/TW tiles of one 128-column slab and
 // writes one partial sum / sum of squares per row and slab, so the workspace layout does not depend on TW.
 template <typename T, bool MEANVAR, bool SR, int TW = 32>
-__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : (TW == 64 ? 2 : 1))
+__global__ void __launch_bounds__(THREADS, TW == 32 ? 3 : 2)
 add_kernel(const T* __restrict__ x1, const int8_t* __restrict__ q2, const __half* __restrict__ s2, int64_t M, int64_t N,
            float* __restrict__ y1, int8_t* __restrict__ qy, __half* __restrict__ sy, float* __restrict__ part_sum,
            float* __restrict__ part_sq, SrCfg sr) {
@@ -862,53 +952,61 @@ static inline int check_mn(int64_t M, int64_t N) {
     return (mult32(M) && mult32(N) && (M / 32) * (N / 32) < (int64_t(1) << 31)) ? JF_OK : JF_ERR_SHAPE;
 }
 
-// CTAs of a persistent launch: two per SM (the streaming kernels fit two 8-warp CTAs per SM; one that fits only one simply runs
-// its second half afterwards).
-static int persistent_ctas() {
-    static const int n = [] {
-        int dev = 0, sms = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        return 2 * sms;
+// CTAs of a persistent launch: `per_sm` 8-warp CTAs per SM (3 for the 32-column kernels at <= 80 registers, 2 otherwise).
+static int persistent_ctas(int per_sm) {
+    static const int sms = [] {
+        int dev = 0, n = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        return n;
     }();
-    return n;
+    return per_sm * sms;
 }
 
-// Tile width of the single-input streaming kernels: 64 by default; JF_NL_TW=128 selects the wide tile (tuning only).
-static int narrow_tw() {
-    static const int tw = [] { const char* e = getenv("JF_NL_TW"); return (e && atoi(e) == 128) ? 128 : 64; }();
-    return tw;
-}
-#define JF_TW_DISPATCH(CALL64, CALL128) \
-    do {                                \
-        if (narrow_tw() != 128) { CALL64; } else { CALL128; } \
-    } while (0)
-// The instruction-bound kernels (GELU forward / backward, LayerNorm forward) default to 32-column tiles: half the registers
-// (80 instead of 128, three CTAs per SM) and half the unrolled code measured 7-10 % faster than 64-column tiles.
-static int compute_tw() {
-    static const int tw = [] { const char* e = getenv("JF_NL_TW"); const int v = e ? atoi(e) : 32; return (v == 128 || v == 64) ? v : 32; }();
-    return tw;
-}
-#define JF_TW3_DISPATCH(CALL32, CALL64, CALL128) \
-    do {                                \
-        if (compute_tw() == 32) { CALL32; } else if (compute_tw() == 64) { CALL64; } else { CALL128; } \
-    } while (0)
-
-static bool quant_tw32() {
-    static const bool v = [] { const char* e = getenv("JF_QUANT_TW"); return !(e && atoi(e) == 64); }();   // default: 32-column tiles
-    return v;
-}
-template <typename T, int TW>
+// Tile widths (measured choices): 32 columns for the kernels with arithmetic per element (quantize without the transposed
+// copy, GELU, LayerNorm forward, residual add), 64 for the pure data movers (dequantize, transpose, quantize + transposed copy).
+template <typename T>
 static void launch_quantize(const void* x, int64_t M, int64_t N, int8_t* q, __half* s, int8_t* qt, bool stochastic, SrCfg sr,
                             cudaStream_t st) {
-    const unsigned grid = grid_for<TW>(M, N, TW == 32 ? persistent_ctas() * 3 / 2 : persistent_ctas());
     const T* xp = (const T*)x;
     if (qt) {
-        if (stochastic) quantize_kernel<T, TW, true, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
-        else quantize_kernel<T, TW, false, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
+        const unsigned grid = grid_for<64>(M, N, persistent_ctas(2));
+        if (stochastic) quantize_kernel<T, 64, true, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
+        else quantize_kernel<T, 64, false, true><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, qt, sr);
     } else {
-        if (stochastic) quantize_kernel<T, TW, true, false><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, nullptr, sr);
-        else quantize_kernel<T, TW, false, false><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, nullptr, sr);
+        const unsigned grid = grid_for<32>(M, N, persistent_ctas(3));
+        if (stochastic) quantize_kernel<T, 32, true, false><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, nullptr, sr);
+        else quantize_kernel<T, 32, false, false><<<grid, THREADS, 0, st>>>(xp, M, N, q, s, nullptr, sr);
     }
+}
+
+// The GELU-forward table of the current device: filled by one kernel launch on the first call's stream; until that launch is
+// known to have finished, calls on any stream wait for its event.
+struct FwdTableState {
+    cudaEvent_t ready = nullptr;
+    bool launched = false, complete = false;
+};
+static FwdTableState g_fwd_table[64];
+static std::mutex g_fwd_table_mutex;
+
+static int ensure_gelu_fwd_table(cudaStream_t st) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JF_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_fwd_table_mutex);
+    FwdTableState& ts = g_fwd_table[dev];
+    if (ts.complete) return JF_OK;
+    if (!ts.launched) {
+        if (cudaEventCreateWithFlags(&ts.ready, cudaEventDisableTiming) != cudaSuccess) return JF_ERR_LAUNCH;
+        gelu_fwd_table_kernel<<<256, 256, 0, st>>>();
+        if (int e = check_launch()) return e;
+        if (cudaEventRecord(ts.ready, st) != cudaSuccess) return JF_ERR_LAUNCH;
+        ts.launched = true;
+        return JF_OK;   // later work on `st` is ordered after the fill
+    }
+    if (cudaEventQuery(ts.ready) == cudaSuccess) {
+        ts.complete = true;
+        return JF_OK;
+    }
+    return cudaStreamWaitEvent(st, ts.ready, 0) == cudaSuccess ? JF_OK : JF_ERR_LAUNCH;
 }
 
 template <typename T>
@@ -951,12 +1049,9 @@ int jf_int8_quantize(const void* x, int x_dtype, int64_t M, int64_t N, int8_t* q
     __half* sh = (__half*)s;
     const bool sto = stochastic != 0;
     switch (x_dtype) {
-        case JF_F32: if (!qt && quant_tw32()) { launch_quantize<float, 32>(x, M, N, q, sh, qt, sto, sr, st); break; }
-                     JF_TW_DISPATCH((launch_quantize<float, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<float, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
-        case JF_F16: if (!qt && quant_tw32()) { launch_quantize<__half, 32>(x, M, N, q, sh, qt, sto, sr, st); break; }
-                     JF_TW_DISPATCH((launch_quantize<__half, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__half, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
-        case JF_BF16: if (!qt && quant_tw32()) { launch_quantize<__nv_bfloat16, 32>(x, M, N, q, sh, qt, sto, sr, st); break; }
-                      JF_TW_DISPATCH((launch_quantize<__nv_bfloat16, 64>(x, M, N, q, sh, qt, sto, sr, st)), (launch_quantize<__nv_bfloat16, 128>(x, M, N, q, sh, qt, sto, sr, st))); break;
+        case JF_F32: launch_quantize<float>(x, M, N, q, sh, qt, sto, sr, st); break;
+        case JF_F16: launch_quantize<__half>(x, M, N, q, sh, qt, sto, sr, st); break;
+        case JF_BF16: launch_quantize<__nv_bfloat16>(x, M, N, q, sh, qt, sto, sr, st); break;
         default: return JF_ERR_DTYPE;
     }
     return check_launch();
@@ -967,8 +1062,7 @@ int jf_int8_dequantize(const int8_t* q, const void* s, int64_t M, int64_t N, flo
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(q); JF_REQUIRE_ALIGNED(y);
     cudaStream_t st = (cudaStream_t)stream;
-    JF_TW_DISPATCH((dequantize_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(q, (const __half*)s, M, N, y)),
-                   (dequantize_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(q, (const __half*)s, M, N, y)));
+    dequantize_kernel<64><<<grid_for<64>(M, N, persistent_ctas(2)), THREADS, 0, st>>>(q, (const __half*)s, M, N, y);
     return check_launch();
 }
 
@@ -977,8 +1071,7 @@ int jf_int8_transpose(const int8_t* x, int64_t M, int64_t N, int8_t* y, void* st
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(x); JF_REQUIRE_ALIGNED(y);
     cudaStream_t st = (cudaStream_t)stream;
-    JF_TW_DISPATCH((transpose_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(x, M, N, y)),
-                   (transpose_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(x, M, N, y)));
+    transpose_kernel<64><<<grid_for<64>(M, N, persistent_ctas(2)), THREADS, 0, st>>>(x, M, N, y);
     return check_launch();
 }
 
@@ -987,9 +1080,8 @@ int jf_int8_gelu_forward(const int8_t* qx, const void* sx, int64_t M, int64_t N,
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qy);
     cudaStream_t st = (cudaStream_t)stream;
-    JF_TW3_DISPATCH((gelu_fwd_kernel<32><<<grid_for<32>(M, N, persistent_ctas() * 3 / 2), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy)),
-                   (gelu_fwd_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy)),
-                   (gelu_fwd_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy)));
+    if (int e = ensure_gelu_fwd_table(st)) return e;
+    gelu_fwd_kernel<<<grid_for<32>(M, N, persistent_ctas(3)), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy);
     return check_launch();
 }
 
@@ -1002,14 +1094,9 @@ int jf_int8_gelu_backward(const int8_t* qx, const void* sx, const int8_t* qg, co
     SrCfg sr = make_sr(noise, seed, offset);
     cudaStream_t st = (cudaStream_t)stream;
     const __half* sxh = (const __half*)sx; const __half* sgh = (const __half*)sg; __half* sdh = (__half*)sd;
-    if (stochastic) {
-        JF_TW3_DISPATCH((gelu_bwd_kernel<32, true><<<grid_for<32>(M, N, persistent_ctas() * 3 / 2), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)),
-                       (gelu_bwd_kernel<64, true><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)),
-                       (gelu_bwd_kernel<128, true><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)));
-    } else {
-        JF_TW_DISPATCH((gelu_bwd_kernel<64, false><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)),
-                       (gelu_bwd_kernel<128, false><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr)));
-    }
+    const unsigned grid = grid_for<32>(M, N, persistent_ctas(3));
+    if (stochastic) gelu_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr);
+    else gelu_bwd_kernel<false><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr);
     return check_launch();
 }
 
@@ -1020,9 +1107,7 @@ int jf_int8_layernorm_forward(const int8_t* qx, const void* sx, const float* gam
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qy); JF_REQUIRE_ALIGNED(gamma);
     cudaStream_t st = (cudaStream_t)stream;
-    JF_TW3_DISPATCH((ln_fwd_kernel<32><<<grid_for<32>(M, N, persistent_ctas() * 3 / 2), THREADS, 0, st>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy, (__half*)sy)),
-                   (ln_fwd_kernel<64><<<grid_for<64>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy, (__half*)sy)),
-                   (ln_fwd_kernel<128><<<grid_for<128>(M, N, persistent_ctas()), THREADS, 0, st>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy, (__half*)sy)));
+    ln_fwd_kernel<32><<<grid_for<32>(M, N, persistent_ctas(3)), THREADS, 0, st>>>(qx, (const __half*)sx, gamma, mean, rstd, M, N, qy, (__half*)sy);
     return check_launch();
 }
 
@@ -1040,16 +1125,10 @@ int jf_int8_layernorm_backward(const int8_t* qx, const void* sx, const int8_t* q
     cudaStream_t st = (cudaStream_t)stream;
     SrCfg sr = make_sr(noise, seed, offset);
     const int64_t slab_tiles = (M / QB) * ((N + 127) / 128);
-    static const int wps = [] { const char* e = getenv("JF_LNB_TW"); return (e && atoi(e) == 32) ? 4 : 2; }();   // warps per slab tile
-    const unsigned grid = (unsigned)((slab_tiles + WARPS / wps - 1) / (WARPS / wps));
+    const unsigned grid = (unsigned)((slab_tiles + WARPS / 2 - 1) / (WARPS / 2));   // two warps per 32 x 128 slab tile
     const __half* sxh = (const __half*)sx; const __half* sgh = (const __half*)sg; __half* sdh = (__half*)sd;
-    if (wps == 4) {
-        if (stochastic) ln_bwd_kernel<true, 32><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
-        else ln_bwd_kernel<false, 32><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
-    } else {
-        if (stochastic) ln_bwd_kernel<true, 64><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
-        else ln_bwd_kernel<false, 64><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
-    }
+    if (stochastic) ln_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
+    else ln_bwd_kernel<false><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, gamma, mean, rstd, M, N, qd, sdh, scratch, sr);
     if (int e = check_launch()) return e;
     ln_bwd_dw_kernel<<<(unsigned)((N + 31) / 32), 256, 0, st>>>(scratch, M / QB, N, dgamma);
     return check_launch();

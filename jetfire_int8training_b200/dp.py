@@ -51,6 +51,65 @@ def allreduce_mean_(tensors, group=None, bucket_bytes=None):
     return tensors
 
 
+class OverlappedMeanReducer:
+    """Mean of the weight gradients across ranks, off the compute stream.
+
+    The weight gradient of step i is only needed by the optimiser, not by the forward / input-gradient GEMMs of step i+1, so its
+    all-reduce does not have to sit between the steps: submit() makes a side stream wait for the gradients (an event on the
+    current stream) and issues the collective there; wait() makes the current stream wait for every collective submitted so
+    far.  On NCCL the division by the world size is folded into the collective (ReduceOp.AVG); gloo (the CPU tests) has no AVG,
+    there the sum is divided afterwards.  With one rank (or no process group) both calls do nothing.
+    """
+
+    def __init__(self, group=None, device=None):
+        self.group = group
+        self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if self.active else 1
+        self.cuda = bool(self.active and device is not None and torch.device(device).type == "cuda")
+        self.stream = torch.cuda.Stream(device) if self.cuda else None
+        self.avg = self.active and dist.get_backend(group) == "nccl"
+        self.pending = []        # (tensors, done event or None)
+
+    def submit(self, tensors):
+        if not self.active:
+            return
+        tensors = [t for t in tensors]
+        if self.cuda:
+            ready = torch.cuda.Event()
+            ready.record()                                   # the gradients are complete at this point of the current stream
+            with torch.cuda.stream(self.stream):
+                self.stream.wait_event(ready)
+                self._reduce(tensors)
+                done = torch.cuda.Event()
+                done.record(self.stream)
+            for t in tensors:
+                t.record_stream(self.stream)                 # the caching allocator must not reuse them before the collective ran
+            self.pending.append((tensors, done))
+        else:
+            self._reduce(tensors)
+            self.pending.append((tensors, None))
+
+    def _reduce(self, tensors):
+        for t in tensors:
+            flat = t if t.is_contiguous() else None
+            assert flat is not None, "gradients are reduced in place and must be contiguous"
+            if self.avg:
+                dist.all_reduce(t, op=dist.ReduceOp.AVG, group=self.group)
+            else:
+                dist.all_reduce(t, group=self.group)
+                t.div_(self.world)
+
+    def wait(self):
+        """Order the current stream after every submitted collective; returns the reduced tensors in submission order."""
+        out = []
+        for tensors, done in self.pending:
+            if done is not None:
+                torch.cuda.current_stream().wait_event(done)
+            out.extend(tensors)
+        self.pending = []
+        return out
+
+
 def shard_range(total, rank, world):
     """Contiguous [begin, end) share of `total` items for `rank` (the first total % world ranks get one more)."""
     base, rem = divmod(total, world)

@@ -9,8 +9,8 @@ only tracks floating tensors.  Attention itself (scaled-dot-product), the embedd
 in floating point, as they do in the reference.
 
 Differences from the reference's module, none of which touch the operators' semantics: weight gradients are produced in fp32
-(the reference's fp16 overflows under its 2^24 loss scale), and the materialised dY^T copies are not made (the GEMMs read dY
-in place).
+(the reference's fp16 overflows under its 2^24 loss scale), the materialised dY^T copies are not made (the GEMMs read dY
+in place), and a weight is quantised once per value (cached until the optimiser changes it) instead of once per forward pass.
 """
 import math
 from dataclasses import dataclass
@@ -37,6 +37,22 @@ class GPTConfig:
 
 def _f8(t):
     return t.view(F8)
+
+
+def quantized_weight(w):
+    """(int8 payload, fp16 scales) of a weight matrix, cached on the parameter until the parameter changes.
+
+    The reference re-quantises every weight in every forward pass (INT8_GPT2/qmodel.py:92, 139, 199-200); with gradient
+    accumulation that is the same quantisation of the same values once per micro-step.  The cache key is the tensor's
+    version counter, which every in-place update (the optimiser step, a checkpoint load) advances, together with its storage
+    address; round-to-nearest quantisation is deterministic, so a cached result is bit-identical to a fresh one."""
+    key = (w._version, w.data_ptr())
+    hit = getattr(w, "_jf_qcache", None)
+    if hit is not None and hit[0] == key:
+        return hit[1], hit[2]
+    qw, sw = NL.int8_quantize(w.detach(), QB)
+    w._jf_qcache = (key, qw, sw)
+    return qw, sw
 
 
 def _i8(t):
@@ -77,7 +93,7 @@ class _AttnIn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, residual, qx, sx, w_qkv, ln_w, mean, rstd):
         qx = _i8(qx)
-        qw, sw = NL.int8_quantize(w_qkv, QB)
+        qw, sw = quantized_weight(w_qkv)
         qn, sn, _ = NL.int8_layernorm_forward(qx, sx, ln_w, mean, rstd, QB)
         y = L.int8_linear_forward(qn, sn, qw, sw, False, QB)
         ctx.save_for_backward(qx, sx, qn, sn, qw, sw, ln_w, mean, rstd)
@@ -98,7 +114,7 @@ class _AttnOut(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, residual, y, w_proj):
-        qw, sw = NL.int8_quantize(w_proj, QB)
+        qw, sw = quantized_weight(w_proj)
         qy, sy = NL.int8_quantize(y.contiguous(), QB)
         qo, so = L.int8_linear_forward(qy, sy, qw, sw, True, QB)
         fpx, qx, sx, mean, rstd = NL.int8_add_Ifp_Ig16_Ofp_Og_MeanVar(residual.contiguous(), qo, so, QB)
@@ -119,8 +135,8 @@ class _MLP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, residual, qx, sx, w1, w2, ln_w, mean, rstd):
         qx = _i8(qx)
-        qw1, sw1 = NL.int8_quantize(w1, QB)
-        qw2, sw2 = NL.int8_quantize(w2, QB)
+        qw1, sw1 = quantized_weight(w1)
+        qw2, sw2 = quantized_weight(w2)
         qn, sn, _ = NL.int8_layernorm_forward(qx, sx, ln_w, mean, rstd, QB)
         qh, sh = L.int8_linear_forward(qn, sn, qw1, sw1, True, QB)
         qa, sa = NL.int8_gelu_forward(qh, sh, QB)

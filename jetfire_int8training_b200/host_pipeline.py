@@ -23,6 +23,8 @@ class LinearStepPipeline:
         self.dev = torch.device(device)
         self.stochastic = stochastic
         self.after_backward = after_backward
+        # The compute stream is the stream that is current when the pipeline is built; submit() runs its GEMMs on it whatever
+        # stream is current at that time, because all of the pipeline's events are ordered against this one stream.
         self.s_comp = torch.cuda.current_stream(self.dev)
         self.s_in = torch.cuda.Stream(self.dev)
         self.s_out = torch.cuda.Stream(self.dev)
@@ -33,10 +35,16 @@ class LinearStepPipeline:
         self.last_out = None
 
     def _h2d(self, i, host_in):
-        if self.dev_in[i % 2] is None:
-            self.dev_in[i % 2] = [torch.empty_like(t, device=self.dev) for t in host_in]
-        buf = self.dev_in[i % 2]
         with torch.cuda.stream(self.s_in):
+            if self.dev_in[i % 2] is None:
+                # Allocated under the copy stream, so the caching allocator hands out memory that is free with respect to THIS
+                # stream.  Its first use is still ordered after everything queued on the compute stream so far: a block that the
+                # allocator recycled from the compute stream may be read by kernels that are still queued there.
+                first = torch.cuda.Event()
+                first.record(self.s_comp)
+                self.s_in.wait_event(first)
+                self.dev_in[i % 2] = [torch.empty_like(t, device=self.dev) for t in host_in]
+            buf = self.dev_in[i % 2]
             if self.free_ev[i % 2] is not None:
                 self.s_in.wait_event(self.free_ev[i % 2])
             for d, h in zip(buf[:4], host_in[:4]):          # forward operands first, so that the forward GEMM can start
@@ -57,14 +65,17 @@ class LinearStepPipeline:
         self.prefetched = (i + 1, self._h2d(i + 1, next_host_in)) if next_host_in is not None else None
         x8, sx, w8, sw, g8, sg = self.dev_in[i % 2]
         s_comp, s_out = self.s_comp, self.s_out
-        s_comp.wait_event(ev_fwd)
-        y8, sy = Linear.int8_linear_forward(x8, sx, w8, sw, True, 32)
-        ev_y = torch.cuda.Event(); ev_y.record(s_comp)
-        s_comp.wait_event(ev_bwd)
-        gx8, gsx, gw = Linear.int8_linear_backward(x8, sx, g8, sg, None, w8, sw, 32, stochastic=self.stochastic)
-        if self.after_backward is not None:
-            self.after_backward(gw)
-        ev_b = torch.cuda.Event(); ev_b.record(s_comp)
+        with torch.cuda.stream(s_comp):      # the operators launch on the current stream: make it the pipeline's compute stream
+            for d in self.dev_in[i % 2]:
+                d.record_stream(s_comp)      # allocated under the copy stream, read here
+            s_comp.wait_event(ev_fwd)
+            y8, sy = Linear.int8_linear_forward(x8, sx, w8, sw, True, 32)
+            ev_y = torch.cuda.Event(); ev_y.record(s_comp)
+            s_comp.wait_event(ev_bwd)
+            gx8, gsx, gw = Linear.int8_linear_backward(x8, sx, g8, sg, None, w8, sw, 32, stochastic=self.stochastic)
+            if self.after_backward is not None:
+                self.after_backward(gw)
+            ev_b = torch.cuda.Event(); ev_b.record(s_comp)
         self.free_ev[i % 2] = ev_b
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_y)

@@ -22,6 +22,7 @@
  *   SA(i,p) = SA[i*sa_si + p*sa_sp],  SB(j,p) = SB[j*sb_sj + p*sb_sp]     (fp16 bit patterns)
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -136,4 +137,48 @@ void jf_oracle_sum_partials(const float* partials, int64_t splits, int64_t count
         for (int64_t k = 1; k < splits; ++k) s = s + partials[k * count + i];
         out[i] = s;
     }
+}
+
+/* Thread control for the timed CPU baseline: launchers such as torchrun export OMP_NUM_THREADS=1, which would silently turn the
+ * "all host cores" baseline into a single-threaded one. */
+void jf_oracle_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int jf_oracle_max_threads(void) { return omp_get_max_threads(); }
+
+/* RN(a / b) by the sequence the CUDA kernels use for their re-quantising divisions (Markstein's correction step with the
+ * correctly rounded reciprocal):  y = RN(1/b);  q0 = RN(a*y);  r = fma(-b, q0, a);  q = fma(r, y, q0).
+ * Exposed so that a CPU test can compare it with the IEEE quotient on hard operands. */
+float jf_oracle_markstein_div(float a, float b) {
+    const float y = 1.0f / b;
+    const float q0 = a * y;
+    const float r = fmaf(-b, q0, a);
+    return fmaf(r, y, q0);
+}
+/* Number of mismatches between the sequence above and a / b over `count` pairs (arrays a, b). */
+int64_t jf_oracle_markstein_mismatches(const float* a, const float* b, int64_t count) {
+    int64_t bad = 0;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t i = 0; i < count; ++i) {
+        const float q = jf_oracle_markstein_div(a[i], b[i]);
+        const float want = a[i] / b[i];
+        uint32_t uq, uw;
+        memcpy(&uq, &q, 4);
+        memcpy(&uw, &want, 4);
+        bad += (uq != uw);
+    }
+    return bad;
+}
+/* The same, for ONE divisor and every dividend mantissa: dividends m * 2^e for all 2^23 mantissas m in [2^23, 2^24). */
+int64_t jf_oracle_markstein_sweep_mantissas(float b, int e) {
+    int64_t bad = 0;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t m = (1 << 23); m < (1 << 24); ++m) {
+        const float a = ldexpf((float)m, e);
+        const float q = jf_oracle_markstein_div(a, b);
+        const float want = a / b;
+        uint32_t uq, uw;
+        memcpy(&uq, &q, 4);
+        memcpy(&uw, &want, 4);
+        bad += (uq != uw);
+    }
+    return bad;
 }

@@ -61,11 +61,39 @@ def _c():
         lib.jf_oracle_requant.argtypes = [vp, i64, i64, vp, vp, vp, vp]
         lib.jf_oracle_to_half.argtypes = [vp, i64, vp]
         lib.jf_oracle_sum_partials.argtypes = [vp, i64, i64, vp]
+        lib.jf_oracle_set_threads.argtypes = [ctypes.c_int]
+        lib.jf_oracle_set_threads.restype = None
+        lib.jf_oracle_max_threads.restype = ctypes.c_int
+        lib.jf_oracle_markstein_div.argtypes = [ctypes.c_float, ctypes.c_float]
+        lib.jf_oracle_markstein_div.restype = ctypes.c_float
+        lib.jf_oracle_markstein_mismatches.argtypes = [vp, vp, i64]
+        lib.jf_oracle_markstein_mismatches.restype = i64
+        lib.jf_oracle_markstein_sweep_mantissas.argtypes = [ctypes.c_float, ctypes.c_int]
+        lib.jf_oracle_markstein_sweep_mantissas.restype = i64
         for f in (lib.jf_oracle_gemm_accumulate, lib.jf_oracle_gemm_int32, lib.jf_oracle_requant,
                   lib.jf_oracle_to_half, lib.jf_oracle_sum_partials):
             f.restype = None
         _clib = lib
     return _clib
+
+
+def set_threads(n):
+    """Number of OpenMP threads of the C part (launchers like torchrun export OMP_NUM_THREADS=1); returns the value in effect."""
+    _c().jf_oracle_set_threads(int(n))
+    return int(_c().jf_oracle_max_threads())
+
+
+def markstein_mismatches(a, b):
+    """How many of the quotients a[i] / b[i] the CUDA kernels' exact-division sequence gets wrong (expected: none)."""
+    a = np.ascontiguousarray(a, dtype=f32)
+    b = np.ascontiguousarray(b, dtype=f32)
+    assert a.shape == b.shape
+    return int(_c().jf_oracle_markstein_mismatches(_ptr(a), _ptr(b), a.size))
+
+
+def markstein_sweep_mantissas(b, e=0):
+    """Mismatches over all 2^23 dividend mantissas (times 2^e) for the divisor b."""
+    return int(_c().jf_oracle_markstein_sweep_mantissas(float(np.float32(b)), int(e)))
 
 
 def _ptr(a):
@@ -165,6 +193,17 @@ def _div(a, b):
         return (a / b).astype(f32)
 
 
+def _exp32(x):
+    """Correctly rounded fp32 exponential (evaluated in fp64, rounded once).  numpy's own float32 exp is a SIMD
+    approximation whose last bit depends on the host CPU; the oracle must not."""
+    return np.exp(np.asarray(x, dtype=np.float64)).astype(f32)
+
+
+def _erf32(x):
+    """Correctly rounded fp32 error function (fp64 evaluation rounded once; scipy's float32 loop does the same)."""
+    return scipy.special.erf(np.asarray(x, dtype=np.float64)).astype(f32)
+
+
 def _as2d(x):
     x = np.asarray(x)
     return x.reshape(-1, x.shape[-1])
@@ -213,7 +252,7 @@ def int8_gelu_forward(q, s):
     """Jetfire/Nonlinear/gelu_fwd.py:34-126: fp16 dequant, erf GELU in fp32, amax + 5e-5, IEEE divide, RNE."""
     x = _deq16(_as2d(q), _as2d(s)).astype(f32)
     sqrt2 = np.sqrt(f32(2.0))
-    cdf = ((f32(1.0) + scipy.special.erf((x / sqrt2).astype(f32)).astype(f32)) / f32(2.0)).astype(f32)
+    cdf = ((f32(1.0) + _erf32((x / sqrt2).astype(f32))) / f32(2.0)).astype(f32)
     y = (cdf * x).astype(f32)
     amax = (_amax(y) + f32(5e-5)).astype(f32)
     sc = (amax / f32(127.0)).astype(f32)
@@ -225,9 +264,9 @@ def int8_gelu_backward(qx, sx, qg, sg, noise=None):
     x = _deq32(_as2d(qx), _as2d(sx))
     g = _deq32(_as2d(qg), _as2d(sg))
     sqrt2 = np.sqrt(f32(2.0))
-    cdf = (f32(0.5) * (f32(1.0) + scipy.special.erf((x / sqrt2).astype(f32)).astype(f32))).astype(f32)
+    cdf = (f32(0.5) * (f32(1.0) + _erf32((x / sqrt2).astype(f32)))).astype(f32)
     sqrt2pi = np.sqrt(f32(2 * 3.141592653589793))
-    e = np.exp((-(x * x).astype(f32) / f32(2.0)).astype(f32)).astype(f32)
+    e = _exp32((-(x * x).astype(f32) / f32(2.0)).astype(f32))
     ex = ((x / f32(sqrt2pi)).astype(f32) * e).astype(f32)
     d = ((cdf + ex).astype(f32) * g).astype(f32)
     sc = (_amax(d) / f32(127.0)).astype(f32)
@@ -246,15 +285,46 @@ def int8_layernorm_forward(q, s, gamma, mean, rstd):
     return _to_int8_rne(_unblk(_div(_blk(y), _bc(sc)))), sc.astype(f16)
 
 
-def int8_layernorm_backward(qx, sx, qg, sg, gamma, mean, rstd, noise=None, slab=128, dw_accum="fp16"):
+def _seq_sum_last(a):
+    """((a0 + a1) + a2) + ... along the last axis, one fp32 rounding per step."""
+    acc = a[..., 0].astype(f32)
+    for j in range(1, a.shape[-1]):
+        acc = (acc + a[..., j]).astype(f32)
+    return acc
+
+
+def _tree8(a):
+    """((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7)) along the last axis (length 8), fp32."""
+    p = (a[..., 0::2] + a[..., 1::2]).astype(f32)
+    p = (p[..., 0::2] + p[..., 1::2]).astype(f32)
+    return (p[..., 0] + p[..., 1]).astype(f32)
+
+
+def _slab_sums(a, slab, order):
+    """Row sums of a [M, nsl*slab] fp32 array over each slab.  order="numpy": numpy's pairwise summation (what the Triton
+    interpreter, and therefore the golden vectors, use); order="kernel": the CUDA kernel's order -- each 16-column chunk summed
+    left to right, the eight chunks of a 128-column slab combined as a balanced tree (the reference's GPU lowering of tl.sum
+    is a shuffle tree as well; the reference itself leaves the order undefined)."""
+    M = a.shape[0]
+    nsl = a.shape[1] // slab
+    if order == "numpy":
+        return a.reshape(M, nsl, slab).sum(-1, dtype=f32)
+    assert slab == 128, "the kernel order is defined for the reference's 128-column slab"
+    return _tree8(_seq_sum_last(a.reshape(M, nsl, 8, 16)))
+
+
+def int8_layernorm_backward(qx, sx, qg, sg, gamma, mean, rstd, noise=None, slab=128, dw_accum="fp16", order="numpy"):
     """Jetfire/Nonlinear/layernorm.py:197-428 (wrapper :467-526).
 
     Rounding points of the reference: mean, rstd -> fp16; x and dy dequantised in fp16; xhat in fp16;
     wdy = gamma*dy, c1, c2 in fp32 with the row sums taken over each `slab`-column slab only but divided
     by the full N; dx -> fp16; scale = fp32(amax16)/127 and quotient in fp32; dgamma partials per 32 rows
     summed in fp16 (dw_accum="fp16") then across partials in fp32.  slab=None sums over the row.
-    Sum order inside a slab is not defined by the reference (tree reduction on the GPU), so payload
-    parity against it is tolerance-level.
+
+    The ORDER of the 128-term fp32 row sums and of the dgamma column sums is not defined by the reference (tree reductions
+    whose shape the compiler picks).  order="numpy" is the order of the Triton interpreter that produced the golden vectors
+    (bit-exact against them); order="kernel" is the CUDA kernel's documented order and, with dw_accum="kernel", makes the
+    whole operator bit-comparable with the GPU.  Every other rounding point is identical in the two modes.
     Returns (qdx, sdx, dgamma)."""
     qx, sx, qg, sg = _as2d(qx), _as2d(sx), _as2d(qg), _as2d(sg)
     M, N = qx.shape
@@ -270,8 +340,8 @@ def int8_layernorm_backward(qx, sx, qg, sg, gamma, mean, rstd, noise=None, slab=
     # slab is simply shorter -- modelled by zero padding, which does not change the sums.
     nsl = -(-N // slab)
     pad = nsl * slab - N
-    c1 = (np.pad(xw, ((0, 0), (0, pad))).reshape(M, nsl, slab).sum(-1, dtype=f32) / f32(N)).astype(f32)
-    c2 = (np.pad(wdy, ((0, 0), (0, pad))).reshape(M, nsl, slab).sum(-1, dtype=f32) / f32(N)).astype(f32)
+    c1 = (_slab_sums(np.pad(xw, ((0, 0), (0, pad))), slab, order) / f32(N)).astype(f32)
+    c2 = (_slab_sums(np.pad(wdy, ((0, 0), (0, pad))), slab, order) / f32(N)).astype(f32)
     c1 = np.repeat(c1, slab, axis=1)[:, :N]
     c2 = np.repeat(c2, slab, axis=1)[:, :N]
     t = ((xhat.astype(f32) * c1).astype(f32) + c2).astype(f32)
@@ -285,7 +355,19 @@ def int8_layernorm_backward(qx, sx, qg, sg, gamma, mean, rstd, noise=None, slab=
     prod = (dy * xhat).astype(f16)
     if dw_accum == "fp16":   # reference-faithful: each 32-row partial is summed in fp16, partials in fp32
         dw = prod.reshape(M // QB, QB, N).sum(1, dtype=f16).astype(f32).sum(0, dtype=f32)
-    else:                    # what the CUDA kernel does: fp32 accumulation of the fp16 products
+    elif dw_accum == "kernel":
+        # the CUDA kernel: fp32 sums of the fp16 products.  Inside a 32-row tile a lane owns rows rg, rg+8, rg+16, rg+24
+        # (summed in that order), the eight lanes are combined as a balanced tree; the M/32 partial rows are then summed by
+        # eight interleaved groups (rows g, g+8, ...) left to right, and the eight group sums left to right.
+        p32 = prod.astype(f32).reshape(M // QB, 4, 8, N)                       # [tile, pass, rg, col]
+        lane = _seq_sum_last(np.moveaxis(p32, 1, -1))                           # [tile, rg, col]
+        part = _tree8(np.moveaxis(lane, 1, -1))                                 # [tile, col]
+        rows = part.shape[0]
+        grp = np.zeros((8, N), f32)
+        for r in range(rows):
+            grp[r % 8] = (grp[r % 8] + part[r]).astype(f32)
+        dw = _seq_sum_last(np.ascontiguousarray(grp.T))
+    else:                    # plain fp32 accumulation of the fp16 products, numpy order
         dw = prod.astype(f32).reshape(M // QB, QB, N).sum(1, dtype=f32).sum(0, dtype=f32)
     return qd, sc32.astype(f16), dw
 

@@ -32,6 +32,16 @@ def _worker(rank, world, port, q):
     for got, parts in zip(grads, gathered):
         want = sum(p.float() for p in parts) / world
         ok &= torch.allclose(got.float(), want, rtol=2e-3, atol=1e-3)
+    # the overlapped reducer gives the same means (on CPU it runs synchronously; submit / wait keep their contract)
+    from jetfire_int8training_b200.dp import OverlappedMeanReducer
+    red = OverlappedMeanReducer()
+    g2 = [r.contiguous().clone() for r in ref]
+    red.submit(g2[:2]); red.submit(g2[2:])
+    done = red.wait()
+    ok &= len(done) == len(g2) and not red.pending
+    for got, parts in zip(g2, gathered):
+        want = sum(p.float() for p in parts) / world
+        ok &= torch.allclose(got.float(), want, rtol=2e-3, atol=1e-3)
     b, e = shard_range(10, rank, world)
     ok &= (e - b == 5) and (b == 5 * rank)
     q.put((rank, bool(ok)))
@@ -50,6 +60,14 @@ def test_allreduce_mean_two_ranks():
     for p in procs:
         p.join(timeout=60)
     assert sorted(results) == [(0, True), (1, True)]
+
+
+def test_overlapped_reducer_is_a_no_op_without_a_process_group():
+    from jetfire_int8training_b200.dp import OverlappedMeanReducer
+    red = OverlappedMeanReducer()
+    x = torch.ones(4)
+    red.submit([x])
+    assert red.wait() == [] and torch.equal(x, torch.ones(4))
 
 
 def test_shard_range_covers_everything():

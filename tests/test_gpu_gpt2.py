@@ -53,3 +53,20 @@ def test_small_gpt2_trains():
         loss.backward()
         opt.step()
     assert float(loss) < 0.7 * first
+
+
+def test_quantised_weights_are_cached_until_the_parameter_changes():
+    from jetfire_int8training_b200 import Nonlinear as NL
+    from jetfire_int8training_b200.gpt2 import quantized_weight
+    torch.manual_seed(1)
+    w = torch.nn.Parameter(0.02 * torch.randn(256, 128, device=DEV))
+    q1, s1 = quantized_weight(w)
+    q2, s2 = quantized_weight(w)
+    assert q1 is q2 and s1 is s2                                        # second micro-step: no new quantisation
+    fresh_q, fresh_s = NL.int8_quantize(w.detach(), 32)
+    assert torch.equal(q1, fresh_q) and torch.equal(s1, fresh_s)
+    with torch.no_grad():
+        w.mul_(1.5)                                                     # what an optimiser step does: in place, version advances
+    q3, s3 = quantized_weight(w)
+    fresh_q, fresh_s = NL.int8_quantize(w.detach(), 32)
+    assert q3 is not q1 and torch.equal(q3, fresh_q) and torch.equal(s3, fresh_s)

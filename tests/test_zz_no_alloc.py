@@ -61,3 +61,21 @@ def test_noalloc_rejects_shapes_beyond_its_workspace():
     # 2 * M * ceil(N/128) = 2 * 65536 * 16 floats > 1048576: refused before anything is launched
     assert L.jf_int8_add_meanvar_noalloc(p, 0, p, p, 65536, 2048, p, p, p, p, p, None) == -2
     assert L.jf_int8_add_meanvar_noalloc(p, 0, p, p, 48, 128, p, p, p, p, p, None) == -2
+
+
+def test_noalloc_at_exactly_its_limit():
+    """2 * M * ceil(N/128) == 1048576 floats is the last shape the built-in workspace holds: it must run and give the regular
+    entry point's bits; one more block row must be refused."""
+    from jetfire_int8training_b200._lib import lib
+    L = lib()
+    M, N = 524288, 32
+    g = torch.Generator(device=DEV).manual_seed(7)
+    x1 = torch.randn(M, N, generator=g, device=DEV)
+    q2 = torch.randint(-127, 128, (M, N), generator=g, device=DEV, dtype=torch.int8)
+    s2 = (torch.rand(M // 32, N // 32, generator=g, device=DEV) * 0.05 + 1e-3).half()
+    want = _run(L, False, x1, q2, s2)
+    got = _run(L, True, x1, q2, s2)
+    for w, h in zip(want, got):
+        assert torch.equal(w.view(torch.uint8), h.view(torch.uint8))
+    p = x1.data_ptr()
+    assert L.jf_int8_add_meanvar_noalloc(p, 0, p, p, M + 32, N, p, p, p, p, p, None) == -2

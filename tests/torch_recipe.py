@@ -2,7 +2,8 @@
 
 Each function has the name, arguments and return convention of the operator it stands for (the reference's
 Jetfire/Nonlinear/*.py and Jetfire/Linear/*.py), so that `gpt2.QGPT` can be run on it by swapping the two operator modules.
-It is the "reference INT8 recipe" side of the end-to-end loss-curve comparison: same quantisation points, same block size,
+It is the "reference INT8 recipe" side of the end-to-end loss-curve comparison (pinned to the golden vectors of the reference's
+own kernels by tests/test_recipe_golden.py; `noise=` injects a given rounding-noise tensor for that purpose): same quantisation points, same block size,
 same truncation / rounding rules, stochastic rounding from torch's generator (the reference draws torch.uniform_ noise too,
 Jetfire/Nonlinear/quantize.py:143-144).  The GEMMs are evaluated on the dequantised operands in fp64 and rounded to fp32, i.e.
 with exact per-block integer products and an accumulation at least as accurate as the reference's fp32 one.
@@ -30,7 +31,7 @@ def _unflat(y, bs):
     return y if bs is None else y.reshape(bs, -1, y.shape[-1])
 
 
-def _quant(y, stochastic, trunc=False, amax_adj=0.0):
+def _quant(y, stochastic, trunc=False, amax_adj=0.0, noise=None):
     """fp32 [M,N] -> (int8 payload, fp16 scales): quantize.py:73-96 (+ _stochastic_rounding :119-126); add.py:139 truncates."""
     y = y.float()
     b = _blocks(y)
@@ -38,7 +39,7 @@ def _quant(y, stochastic, trunc=False, amax_adj=0.0):
     scale = amax / 127.0
     v = torch.where(scale > 0, b / scale, torch.zeros_like(b))
     if stochastic:
-        noise = torch.rand_like(v) - 0.5
+        noise = (torch.rand_like(v) - 0.5) if noise is None else _blocks(noise.float())
         v = torch.sign(v) * torch.clamp(v.abs() + noise, max=127.0)
     q = torch.trunc(v) if trunc else torch.round(v)
     q = q.clamp(-127, 127).to(torch.int8).reshape(y.shape)
@@ -56,9 +57,9 @@ def _deq(q, s, half_product=False):
 
 
 # ------------------------------------------------------------------------------------------------ Nonlinear
-def int8_quantize(x, B, stochastic=False):
+def int8_quantize(x, B, stochastic=False, noise=None):
     x2, bs = _flat(x)
-    q, s = _quant(x2, stochastic)
+    q, s = _quant(x2, stochastic, noise=noise)
     return _unflat(q, bs), _unflat(s, bs)
 
 
@@ -70,12 +71,12 @@ def int8_gelu_forward(x, s_x, B):
     return _unflat(q, bs), _unflat(s, bs)
 
 
-def int8_gelu_backward(x, s_x, g, s_g, B, stochastic=False):
+def int8_gelu_backward(x, s_x, g, s_g, B, stochastic=False, noise=None):
     x2, bs = _flat(x); sx2, _ = _flat(s_x); g2, _ = _flat(g); sg2, _ = _flat(s_g)
     v, gv = _deq(x2, sx2), _deq(g2, sg2)
     cdf = 0.5 * (1.0 + torch.erf(v * 0.7071067811865476))
     pdf = torch.exp(-0.5 * v * v) * 0.3989422804014327
-    q, s = _quant((cdf + v * pdf) * gv, stochastic)                   # gelu_bwd.py:101-107
+    q, s = _quant((cdf + v * pdf) * gv, stochastic, noise=noise)      # gelu_bwd.py:101-107
     return _unflat(q, bs), _unflat(s, bs)
 
 
@@ -87,7 +88,7 @@ def int8_layernorm_forward(x, sx, weight, mean, rstd, B, eps=1e-6):
     return _unflat(q, bs), _unflat(s, bs), (mean, rstd)
 
 
-def int8_layernorm_backward(x, sx, g, sg, w, B, m, v, stochastic=False, eps=1e-6):
+def int8_layernorm_backward(x, sx, g, sg, w, B, m, v, stochastic=False, eps=1e-6, noise=None):
     """layernorm.py:310-336: statistics, x, dy and xhat in fp16; row sums over the 128-column slab divided by N; dx -> fp16."""
     x2, bs = _flat(x); sx2, _ = _flat(sx); g2, _ = _flat(g); sg2, _ = _flat(sg)
     M, N = x2.shape
@@ -104,14 +105,14 @@ def int8_layernorm_backward(x, sx, g, sg, w, B, m, v, stochastic=False, eps=1e-6
     dx = ((padded(wdy) - (padded(xhat) * c1 + c2)) * rs.float().reshape(M, 1, 1)).reshape(M, -1)[:, :N]
     dx = dx.half().float()
     dw = (dy.float() * xhat).sum(0)
-    q, s = _quant(dx, stochastic)
+    q, s = _quant(dx, stochastic, noise=noise)
     return _unflat(q, bs), _unflat(s, bs), dw.to(w.dtype)
 
 
-def int8_add_Ifp_Ig16_Ofp_Og(x1, x2, s_x2, B, stochastic=False):
+def int8_add_Ifp_Ig16_Ofp_Og(x1, x2, s_x2, B, stochastic=False, noise=None):
     a, bs = _flat(x1); q2, _ = _flat(x2); s2, _ = _flat(s_x2)
     y = a.float() + _deq(q2, s2)                                       # add.py:120-139 (truncating cast)
-    q, s = _quant(y, stochastic, trunc=True)
+    q, s = _quant(y, stochastic, trunc=True, noise=noise)
     return _unflat(y, bs), _unflat(q, bs), _unflat(s, bs)
 
 
