@@ -174,8 +174,23 @@ int jf_igemm_wgrad_plan(int64_t M, int64_t N, int64_t K, int split_k);
 int jf_igemm_int32(const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c, void* stream);
 
 /* Reads and clears the device-side flag raised when a bounded wait inside a GEMM kernel expired (0 = none).
- * Diagnostic; synchronises the device.  No counterpart in the reference. */
+ * Synchronises the device, so callers poll it at their own synchronisation points (end of an optimiser step, end of a timed
+ * region): a non-zero value means that GEMM results since the last poll are invalid.  No counterpart in the reference. */
 int jf_igemm_error_flag(void);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Language-model head loss (the caller's un-quantised tail):  F.cross_entropy(logits.view(-1, V), targets.view(-1),
+ * ignore_index=-1) of INT8_GPT2/qmodel.py:433-439, for bf16 logits, without materialising fp32 logits.
+ * forward : lse[r] = log sum_c exp(logits[r, c]);  loss_rows[r] = lse[r] - logits[r, targets[r]]  (0 when targets[r] is outside
+ *           [0, V): an ignored position).  The caller averages loss_rows over the positions that count.
+ * backward: IN PLACE  logits[r, c] <- (exp(logits[r, c] - lse[r]) - [c == targets[r]]) * (*grad_out) * inv_count  as bf16
+ *           (zero rows for ignored positions); `grad_out` is a device pointer to the upstream scalar gradient.
+ * logits: bf16 [rows, V] row-major, 16-byte aligned, V a multiple of 8 (every row 16-byte aligned); targets int64 [rows].
+ * ------------------------------------------------------------------------------------------------------------ */
+int jf_lm_loss_forward(const void* logits_bf16, const int64_t* targets, int64_t rows, int64_t V, float* lse, float* loss_rows,
+                       void* stream);
+int jf_lm_loss_backward(void* logits_bf16, const int64_t* targets, const float* lse, const float* grad_out, float inv_count,
+                        int64_t rows, int64_t V, void* stream);
 
 #ifdef __cplusplus
 }

@@ -34,6 +34,8 @@ SIGNATURES = {
     "jf_igemm_wgrad_plan": ([_i64, _i64, _i64, _int], _int),
     "jf_igemm_int32": ([_vp, _vp, _i64, _i64, _i64, _vp, _vp], _int),
     "jf_igemm_error_flag": ([], _int),
+    "jf_lm_loss_forward": ([_vp, _vp, _i64, _i64, _vp, _vp, _vp], _int),
+    "jf_lm_loss_backward": ([_vp, _vp, _vp, _vp, ctypes.c_float, _i64, _i64, _vp], _int),
 }
 
 _lib = None

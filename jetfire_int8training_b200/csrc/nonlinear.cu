@@ -613,6 +613,25 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
         });
 }
 
+// Correctly rounded fp32 values of the two transcendental functions of the GELU derivative at x >= 0, as the reference's
+// arithmetic defines them:  er = RN(erf(u)) with u = RN(x / sqrt2),  e = RN(exp(a)) with a = RN(-RN(x*x)/2)  (fp32 roundings RN),
+// both evaluated in fp64 and rounded once.  One fp64 exponential serves both: erf(u) = 1 - exp(-u^2) * erfcx(u), and
+// exp(-u^2) = exp(a) * exp(d) with d = -u^2 - a, |d| < 1e-5 (a and -u^2 differ only by the fp32 roundings), exp(d) from three
+// terms of its series.  Below u = 2^-8 the difference 1 - erfc(u) would lose relative accuracy; there the Maclaurin series of erf
+// is used (truncation error u^6/42 < 1e-16 relative).
+__device__ __forceinline__ void gelu_bwd_erf_exp(float x, float& er, float& e) {
+    const float u = __fdiv_rn(x, SQRT2_F);
+    const float a = __fmul_rn(__fmul_rn(x, x), -0.5f);
+    const double ud = (double)u, E = exp((double)a);
+    e = (float)E;
+    const double u2 = ud * ud;
+    const double d = -u2 - (double)a;
+    const double Eu = E * fma(d, fma(d, 0.5, 1.0), 1.0);                                  // exp(-u^2)
+    const double big = 1.0 - Eu * erfcx(ud);
+    const double small = 1.1283791670955126 * ud * fma(u2, fma(u2, 0.1, -0.33333333333333331), 1.0);
+    er = (float)(u < 0.00390625f ? small : big);
+}
+
 // backward: x = q*s, g = qg*sg in fp32; d = (Phi(x) + x*phi(x)) * g; block quantise (+SR).
 // The table holds Phi(x) + x*phi(x) for the 256 payload values of the block.  erf and exp are odd / even in x, so one fp64
 // evaluation of each serves +q and -q: 128 evaluations per block, four per lane.
@@ -639,8 +658,8 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
             for (int j = 0; j < 4; ++j) {
                 const int a = 4 * t.lane + 1 + j;                        // |q| = 1 .. 128
                 const float x = __fmul_rn((float)a, scx);                // exact
-                const float er = (float)erf((double)__fdiv_rn(x, SQRT2_F));
-                const float e = (float)exp((double)__fmul_rn(__fmul_rn(x, x), -0.5f));
+                float er, e;
+                gelu_bwd_erf_exp(x, er, e);
                 const float ex = __fmul_rn(__fdiv_rn(x, SQRT2PI_F), e);
                 if (a < 128) lut[a] = __fadd_rn(__fmul_rn(0.5f, __fadd_rn(1.0f, er)), ex);
                 lut[256 - a] = __fsub_rn(__fmul_rn(0.5f, __fsub_rn(1.0f, er)), ex);

@@ -21,6 +21,7 @@ from torch.nn import functional as F
 
 from . import Linear as L
 from . import Nonlinear as NL
+from .lm_loss import lm_cross_entropy
 
 QB = 32
 F8 = torch.float8_e4m3fn
@@ -222,4 +223,4 @@ class QGPT(nn.Module):
         x = F.layer_norm(x.float(), (self.cfg.n_embd,), self.ln_f, None, 1e-5)
         with torch.autocast("cuda", dtype=torch.bfloat16):
             logits = F.linear(x, self.wte.weight)
-        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+        return lm_cross_entropy(logits, targets)       # no fp32 copy of the [tokens, vocab] logits; gradient written in place

@@ -70,3 +70,26 @@ def test_quantised_weights_are_cached_until_the_parameter_changes():
     q3, s3 = quantized_weight(w)
     fresh_q, fresh_s = NL.int8_quantize(w.detach(), 32)
     assert q3 is not q1 and torch.equal(q3, fresh_q) and torch.equal(s3, fresh_s)
+
+
+@pytest.mark.parametrize("rows,V", [(64, 512), (96, 50304), (33, 1000)])
+def test_lm_cross_entropy_matches_torch(rows, V):
+    """Loss and gradient of the fused LM-head loss against F.cross_entropy on the widened logits.  Tolerances: loss rel-err
+    1e-5 (fp32 reductions in a different order); gradient within one bf16 rounding of torch's fp32 gradient."""
+    from jetfire_int8training_b200.lm_loss import lm_cross_entropy
+    g = torch.Generator(device=DEV).manual_seed(rows + V)
+    logits = (3.0 * torch.randn(rows, V, generator=g, device=DEV)).to(torch.bfloat16)
+    targets = torch.randint(0, V, (rows,), generator=g, device=DEV)
+    targets[::7] = -1                                                  # ignored positions, as ignore_index=-1
+    ref_in = logits.float().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, targets, ignore_index=-1)
+    (2.5 * ref).backward()
+    ours_in = logits.clone().requires_grad_(True)
+    work = ours_in * 1                                                  # an intermediate, like the output of the LM-head matmul
+    loss = lm_cross_entropy(work, targets)
+    assert abs(float(loss) - float(ref)) <= 1e-5 * abs(float(ref))
+    (2.5 * loss).backward()
+    want = ref_in.grad
+    got = ours_in.grad.float()
+    assert torch.all((got - want).abs() <= 2.0 ** -8 * want.abs() + 1e-9)
+    assert torch.count_nonzero(got[::7]) == 0                           # ignored rows get no gradient

@@ -75,12 +75,14 @@ def test_reference_wgrad_and_dgrad_kernels_agree_with_the_oracle(ref_ext, oracle
     print(f"reference wgrad-style kernel vs oracle [{M}x{N}x{K}]: {np.count_nonzero(ulp) / ulp.size:.2e} of fp16 outputs differ, max {ulp.max()} ulp")
     # same sequential fp32 FMA chain, no division in this epilogue: identical up to the compiler's freedom under fast-math
     assert ulp.max() <= 1 and np.count_nonzero(ulp) <= 1e-3 * ulp.size
-    # stochastic kernel: its noise stream is curand's; compare the dequantised result at the reference's tolerance and the scales
+    # stochastic kernel: its noise stream is curand's, so payloads are compared with the round-to-nearest oracle: the same
+    # scales, every payload within one step (stochastic rounding picks floor or ceil), and the mean signed deviation of the
+    # payloads close to zero (unbiased)
     q, s = ref_ext.igemm_output_int_quantize_stochastic(A, Bt, SAt, SBt, M, N, K)
     torch.cuda.synchronize()
     qo, sco = oracle.requant(acc)
     sdiff = np.abs(n(s).view(np.int16).astype(np.int32) - sco.view(np.int16).astype(np.int32)).max()
-    d = np.abs(n(q).astype(np.int32) - qo.astype(np.int32))
-    print(f"reference dgrad kernel vs round-to-nearest oracle: payload max {d.max()} step (stochastic), scales max {sdiff} ulp")
-    assert sdiff <= 1 and d.max() <= 1                               # SR moves a payload by at most one step from RN
-    np.testing.assert_allclose(_deq(n(q), n(s)), _deq(qo, sco), rtol=1e-1, atol=5)
+    dev = n(q).astype(np.int32) - qo.astype(np.int32)
+    print(f"reference dgrad kernel vs round-to-nearest oracle: payload max {np.abs(dev).max()} step (stochastic), "
+          f"mean deviation {dev.mean():+.2e}, scales max {sdiff} ulp")
+    assert sdiff <= 1 and np.abs(dev).max() <= 1 and abs(dev.mean()) < 5e-3
