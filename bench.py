@@ -173,7 +173,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     from jetfire_int8training_b200 import Linear, Nonlinear, rng
-    from jetfire_int8training_b200.dp import OverlappedMeanReducer
+    from jetfire_int8training_b200.dp import MeanReducer
     from jetfire_int8training_b200._lib import lib
     L = lib()
     rng.manual_seed(1234 + rank)
@@ -190,10 +190,8 @@ def run_ours(args):
 
     launches_per_step = 3 + (1 if L.jf_igemm_wgrad_plan(N, K, M, 0) > 1 else 0)
     fwd_ev = []
-    # data-parallel exchange: the mean of dW over the ranks, on a side stream.  The weight gradient of step i is consumed by the
-    # optimiser only, so its all-reduce overlaps the forward and input-gradient GEMMs of step i+1; the step waits for the
-    # previous step's collective right after its own weight gradient (and the timed region ends with a wait for the last one).
-    reducer = OverlappedMeanReducer(device=dev)
+    # data-parallel exchange: the mean of dW over the ranks, one NCCL all-reduce (AVG) per step behind the weight-gradient GEMM
+    reducer = MeanReducer(device=dev)
 
     def step(time_fwd=False):
         if time_fwd:
@@ -203,8 +201,8 @@ def run_ours(args):
         if time_fwd:
             e1.record(); fwd_ev.append((e0, e1))
         gx8, gsx, gw = Linear.int8_linear_backward(X8, SX, G8, SG, None, W8, SW, 32, stochastic=True)
-        reducer.wait()
         reducer.submit([gw])
+        reducer.wait()
         return y8, sy, gx8, gsx, gw
 
     for _ in range(args.warmup):
@@ -222,7 +220,6 @@ def run_ours(args):
     ev0.record()
     for _ in range(args.steps):
         step(time_fwd=True)
-    reducer.wait()                    # the last step's gradient exchange is part of the timed region
     ev1.record()
     torch.cuda.synchronize()
     t_wall1 = time.time()
@@ -630,8 +627,10 @@ def run_gemm_sweep(args):
     torch.cuda.set_device(dev)
     rng.manual_seed(7)
     g = torch.Generator(device=dev).manual_seed(0)
-    shapes = [(n, n, n) for n in (1024, 2048, 4096, 8192, 16384)] + [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768),
-                                                                     (8192, 768, 3072), (4096, 8192, 4096)]
+    # the short GPT-2 layer kernels first: after the seconds-long 16384^3 launches the part runs power-capped at ~1.3 GHz for a
+    # while, which would be charged to whatever shape is measured next
+    shapes = [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072), (4096, 8192, 4096)] + \
+             [(n, n, n) for n in (1024, 2048, 4096, 8192, 16384)]
     # the last shape is the one point the reference publishes: its weight-gradient kernel with M = 8192, N = K = 4096 in the
     # kernel's own terms (out_features 8192 x in_features 4096 over 4096 tokens here): 261.6e12 ops/s, hardware not stated
     PUBLISHED_WGRAD_TOPS = 261.6
@@ -701,6 +700,52 @@ def run_gemm_sweep(args):
                       "shapes": out}), flush=True)
 
 
+def run_reference_gemm_sweep(args):
+    """`--impl reference --workload gemm_sweep`: the reference's OWN GEMM kernels (its WMMA extension rebuilt for sm_100 by
+    oracle/build_ref.py, loaded from oracle/_ref/) timed on this GPU at shapes they support (M, N multiples of 128, N <= 4096):
+    the GPU-side baseline of the sweep.  Prints {"unavailable": ...} when the extension has not been built."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    from oracle import build_ref
+    ext = build_ref.load()
+    if ext is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/BlockQuantizeCUDA.so not built (python oracle/build_ref.py)"}))
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    out = {}
+    # kernel-level shapes (M, N, K) as the reference's own benchmark states them; the first is its published point
+    for (M, N, K) in ((8192, 4096, 4096), (8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072)):
+        A = torch.randint(-127, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+        Bnk = torch.randint(-127, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+        Bkn = torch.randint(-127, 128, (K, N), generator=g, device=dev, dtype=torch.int8)
+        SAt = (torch.rand(K // 32, M // 32, generator=g, device=dev) * 0.099 + 1e-3).half()
+        SBt = (torch.rand(K // 32, N // 32, generator=g, device=dev) * 0.099 + 1e-3).half()
+        bias = torch.zeros(N, device=dev); biasmax = torch.zeros(1, device=dev)
+        calls = {"fwd_rowcol": lambda: ext.igemm_output_int_quantize_bias_rowcol(A, Bnk.t(), bias, biasmax, SAt, SBt, M, N, K),
+                 "dgrad_stochastic": lambda: ext.igemm_output_int_quantize_stochastic(A, Bkn, SAt, SBt, M, N, K),
+                 "wgrad_fp": lambda: ext.igemm_output_fp_no_quantize(A, Bkn, SAt, SBt, M, N, K)}
+        rec = {}
+        for name, fn in calls.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = 10
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record(); torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / n
+            rec[name + "_ms"] = round(ms, 4); rec[name + "_tops"] = round(2.0 * M * N * K / ms / 1e9, 1)
+        out[f"{M}x{N}x{K}"] = rec
+    print(json.dumps({"impl": "reference", "metric": "per-block INT8 GEMM TOPS", "unit": "TOPS",
+                      "what": "the reference's WMMA kernels (JetfireGEMMKernel extension) recompiled for sm_100, -use_fast_math, on this GPU",
+                      "shape": "kernel-level M x N x K", "shapes": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -720,7 +765,9 @@ def main():
     ap.add_argument("--cols", type=int, default=3072)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.impl == "reference" and args.workload == "gemm_sweep":
+        run_reference_gemm_sweep(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "nonlinear":
         run_nonlinear(args)

@@ -51,21 +51,25 @@ def allreduce_mean_(tensors, group=None, bucket_bytes=None):
     return tensors
 
 
-class OverlappedMeanReducer:
-    """Mean of the weight gradients across ranks, off the compute stream.
+class MeanReducer:
+    """Mean of the weight gradients across ranks: submit() issues the collective, wait() orders the current stream after it.
 
-    The weight gradient of step i is only needed by the optimiser, not by the forward / input-gradient GEMMs of step i+1, so its
-    all-reduce does not have to sit between the steps: submit() makes a side stream wait for the gradients (an event on the
-    current stream) and issues the collective there; wait() makes the current stream wait for every collective submitted so
-    far.  On NCCL the division by the world size is folded into the collective (ReduceOp.AVG); gloo (the CPU tests) has no AVG,
-    there the sum is divided afterwards.  With one rank (or no process group) both calls do nothing.
+    On NCCL the division by the world size is folded into the collective (ReduceOp.AVG); gloo (the CPU tests) has no AVG, there
+    the sum is divided afterwards.  With one rank (or no process group) both calls do nothing.
+
+    overlap=False (default): the collective runs on the current stream, right behind the kernel that produced the gradients.
+    overlap=True: it runs on a side stream that waits for the gradients, so that later kernels on the current stream (the next
+    step's forward and input-gradient GEMMs, which do not need the reduced gradient) may run beside it.  Measured on two B200s
+    with the 8192^3 layer this is SLOWER (5.93 ms per step against 5.70 ms): the GEMMs are persistent kernels with one CTA of
+    608 threads x 96 registers per SM, so no SM has room for the collective's CTAs until a GEMM kernel drains, and the two
+    then alternate at kernel granularity with a tail on each switch.  It is kept for callers whose kernels leave SMs free.
     """
 
-    def __init__(self, group=None, device=None):
+    def __init__(self, group=None, device=None, overlap=False):
         self.group = group
         self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.world = dist.get_world_size(group) if self.active else 1
-        self.cuda = bool(self.active and device is not None and torch.device(device).type == "cuda")
+        self.cuda = bool(self.active and overlap and device is not None and torch.device(device).type == "cuda")
         self.stream = torch.cuda.Stream(device) if self.cuda else None
         self.avg = self.active and dist.get_backend(group) == "nccl"
         self.pending = []        # (tensors, done event or None)

@@ -32,9 +32,9 @@ def _worker(rank, world, port, q):
     for got, parts in zip(grads, gathered):
         want = sum(p.float() for p in parts) / world
         ok &= torch.allclose(got.float(), want, rtol=2e-3, atol=1e-3)
-    # the overlapped reducer gives the same means (on CPU it runs synchronously; submit / wait keep their contract)
-    from jetfire_int8training_b200.dp import OverlappedMeanReducer
-    red = OverlappedMeanReducer()
+    # the reducer object gives the same means (submit / wait contract)
+    from jetfire_int8training_b200.dp import MeanReducer
+    red = MeanReducer()
     g2 = [r.contiguous().clone() for r in ref]
     red.submit(g2[:2]); red.submit(g2[2:])
     done = red.wait()
@@ -62,9 +62,9 @@ def test_allreduce_mean_two_ranks():
     assert sorted(results) == [(0, True), (1, True)]
 
 
-def test_overlapped_reducer_is_a_no_op_without_a_process_group():
-    from jetfire_int8training_b200.dp import OverlappedMeanReducer
-    red = OverlappedMeanReducer()
+def test_reducer_is_a_no_op_without_a_process_group():
+    from jetfire_int8training_b200.dp import MeanReducer
+    red = MeanReducer()
     x = torch.ones(4)
     red.submit([x])
     assert red.wait() == [] and torch.equal(x, torch.ones(4))

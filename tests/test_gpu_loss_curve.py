@@ -20,12 +20,13 @@ def recipe_ops():
     """Run gpt2.QGPT on the torch restatement of the operators instead of the CUDA library."""
     import torch_recipe
     from jetfire_int8training_b200 import gpt2
-    saved = gpt2.L, gpt2.NL
+    saved = gpt2.L, gpt2.NL, gpt2.lm_cross_entropy
     gpt2.L = gpt2.NL = torch_recipe
+    gpt2.lm_cross_entropy = lambda logits, t: torch.nn.functional.cross_entropy(logits.float().view(-1, logits.size(-1)), t.view(-1))
     try:
         yield
     finally:
-        gpt2.L, gpt2.NL = saved
+        gpt2.L, gpt2.NL, gpt2.lm_cross_entropy = saved
 
 
 def synthetic_tokens(n_seq, T, vocab, seed):
