@@ -188,7 +188,9 @@ def run_ours(args):
         return (torch.rand(r, c, generator=g, device=dev) * 0.099 + 1e-3).half()
     SX, SW, SG = scales(M // 32, K // 32), scales(N // 32, K // 32), scales(M // 32, N // 32)
 
-    launches_per_step = 3 + (1 if L.jf_igemm_wgrad_plan(N, K, M, 0) > 1 else 0)
+    # forward, dgrad, wgrad (+ the split-K reduction); each GEMM that runs on fp16 operand copies adds its two conversion kernels
+    f16ops = L.jf_igemm_op16_bytes(M, N, K) > 0
+    launches_per_step = (9 if f16ops else 3) + (1 if L.jf_igemm_wgrad_plan(N, K, M, 0) > 1 else 0)
     fwd_ev = []
     # data-parallel exchange: the mean of dW over the ranks, one NCCL all-reduce (AVG) per step behind the weight-gradient GEMM
     reducer = MeanReducer(device=dev)
@@ -373,15 +375,19 @@ def run_ours(args):
                         "serial_value": e2e_serial_val, "serial_ms_per_step": e2e_serial_ms / e2e_steps},
                 "gpu_launches": launches_per_step * args.steps,
                 "clocks": clocks,
-                "roofline": {"bound": "tensor", "kernel": "gemm_kernel<K-major,K-major> (forward)", "achieved": fwd_tops,
+                "roofline": {"bound": "tensor",
+                             "kernel": ("gemm_kernel<fp16 operand copies, kind::f16> (forward; the launch time includes its two int8->fp16 "
+                                        "conversion kernels)") if f16ops else "gemm_kernel<K-major,K-major, kind::i8> (forward)",
+                             "achieved": fwd_tops,
                              "peak": peak_tops, "unit": "TOPS", "frac": fwd_tops / peak_tops,
                              "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
                              "frac_of_nominal_4500": fwd_tops / 4500.0, "cublas_int_mm_tops": int_mm_tops,
                              "avg_launch_ms": fwd_ms,
-                             # the algorithm's own ceiling: every 128x128x32 block product needs 16384 int32->fp32 conversions
-                             # on a 64-lane-per-clock pipe = 256 SM clocks per K block, whatever the tensor core does
-                             "dequant_bound_tops": DEQUANT_BOUND_TOPS(sm_count, clocks),
-                             "frac_of_dequant_bound": fwd_tops / DEQUANT_BOUND_TOPS(sm_count, clocks),
+                             # the algorithm's own ceiling: the CUDA cores owe every 128x128x32 block product 16384 scale FMAs
+                             # (128 lanes per clock: 128 SM clocks per K block) and, on int8 operands, 16384 int32->fp32 conversions
+                             # on a 64-lane-per-clock pipe (256 clocks), whatever the tensor core does
+                             "dequant_bound_tops": DEQUANT_BOUND_TOPS(sm_count, clocks, f16ops),
+                             "frac_of_dequant_bound": fwd_tops / DEQUANT_BOUND_TOPS(sm_count, clocks, f16ops),
                              "traffic": traffic, "traffic_source": traffic_src,
                              "algorithmic_bytes": M * K + N * K + M * N + 2 * (M * K + N * K + M * N) // 1024},
                 "cpu_baseline": cpu, "gemm_error_flag": err, "gpt2": gpt2_rec, "nonlinear": nonlinear_rec}
@@ -390,11 +396,12 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def DEQUANT_BOUND_TOPS(sm_count, clocks):
-    """Throughput at which the int32 -> fp32 conversions of the per-K-block rescale alone saturate their pipe: one 128x128x32
-    block product (2 * 128 * 128 * 32 ops) per 256 clocks per SM, at the SM clock sampled during the run."""
+def DEQUANT_BOUND_TOPS(sm_count, clocks, f16ops):
+    """Throughput at which the per-K-block rescale alone saturates its pipe: one 128x128x32 block product (2 * 128 * 128 * 32 ops)
+    per 256 SM clocks (int8 operands: the int32 -> fp32 conversions) or per 128 SM clocks (fp16 operand copies: the scale FMAs,
+    and equally the two kind::f16 MMAs), at the SM clock sampled during the run."""
     mhz = (clocks or {}).get("sm_mhz") or 1965.0
-    return sm_count * (2.0 * 128 * 128 * 32) / 256.0 * mhz * 1e6 / 1e12
+    return sm_count * (2.0 * 128 * 128 * 32) / (128.0 if f16ops else 256.0) * mhz * 1e6 / 1e12
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE forward launch at M = N = K = 8192 from an ncu capture, keyed by the

@@ -122,6 +122,13 @@ int jf_int8_add_meanvar_noalloc(const void* x1, int x1_dtype, const int8_t* q2, 
  *     I_p = A_blk x B_blk^T (int32),   acc = fma(sa[i,p]*sb[j,p], (float)I_p, acc)   (fp32)
  * and differ in operand layout and epilogue.  Scale tensors are addressed with explicit element strides so both the
  * natural [rows/32, cols/32] layout and the transposed copies the reference passes are accepted without a copy.
+ *
+ * op16 / op16_bytes (all three): optional scratch for exact fp16 copies of both operands, 2 * (M*K + N*K) bytes, 16-byte
+ * aligned.  When it is given (and large enough) the GEMM first writes the two copies ([M,K] and [N,K], transposing where the
+ * operand is stored [K, rows]) and then runs on them with tcgen05.mma kind::f16, whose fp32 accumulator already holds
+ * float(I_p): the consumers skip the int32 -> fp32 conversion that bounds the int8-operand kernel.  Results are bit-identical
+ * either way (every partial sum is an integer below 2^24).  It pays for large GEMMs only (8192^3: 1.75 -> 1.49 ms including the
+ * conversion passes); jf_igemm_op16_bytes says when.  NULL / 0 selects the int8-operand kernel.
  * ---------------------------------------------------------------------------------------------------------- */
 
 /* Output selector of the re-quantising GEMMs. */
@@ -138,7 +145,7 @@ typedef enum {
  * out_mode JF_OUT_INT8: y8 int8 [M,N] and sy fp16 [M/32,N/32];  JF_OUT_DEQUANT_F16: y16 fp16 [M,N] (y8/sy may be NULL). */
 int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t sx_stride_m, int64_t sx_stride_k,
                      const void* sw, int64_t sw_stride_n, int64_t sw_stride_k, int64_t M, int64_t N, int64_t K,
-                     int out_mode, int8_t* y8, void* sy, void* y16, void* stream);
+                     int out_mode, int8_t* y8, void* sy, void* y16, void* op16, int64_t op16_bytes, void* stream);
 
 /* Input gradient  dX[M,N] = dY[M,K] * W[K,N]   (K = out features, N = in features; W is read in place, no transpose).
  * igemm_output_int_quantize_stochastic(X, W, SXt, SW, M, N, K)
@@ -148,7 +155,7 @@ int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t s
 int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_stride_m, int64_t sg_stride_k,
                    const void* sw, int64_t sw_stride_k, int64_t sw_stride_n, int64_t M, int64_t N, int64_t K,
                    int out_mode, int8_t* dx8, void* sdx, void* dx16, int stochastic, const float* noise, uint64_t seed,
-                   uint64_t offset, void* stream);
+                   uint64_t offset, void* op16, int64_t op16_bytes, void* stream);
 
 /* Weight gradient  dW[M,N] = dY^T * X   (K = tokens, M = out features, N = in features).
  * igemm_output_fp_no_quantize(X, W, SXt, SW, M, N, K)
@@ -163,11 +170,15 @@ int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_
  * scratch: fp32 [splits * M * N] workspace, required when the effective split (jf_igemm_wgrad_plan) is > 1. */
 int jf_igemm_wgrad(const int8_t* g, int g_transposed, const int8_t* x, const void* sg, int64_t sg_stride_k,
                    int64_t sg_stride_m, const void* sx, int64_t sx_stride_k, int64_t sx_stride_n, int64_t M, int64_t N,
-                   int64_t K, int out_dtype, void* dw, int split_k, float* scratch, void* stream);
+                   int64_t K, int out_dtype, void* dw, int split_k, float* scratch, void* op16, int64_t op16_bytes, void* stream);
 
 /* Effective split-K the library would use for (M,N,K,split_k) on the current device (>= 1), so that the caller can
  * size `scratch`.  Host-only; launches nothing. */
 int jf_igemm_wgrad_plan(int64_t M, int64_t N, int64_t K, int split_k);
+
+/* Size of the fp16 operand scratch (bytes) for a GEMM of these dimensions if the fp16-operand path is expected to pay for its
+ * conversion passes, else 0.  Host-only; launches nothing.  No counterpart in the reference. */
+int64_t jf_igemm_op16_bytes(int64_t M, int64_t N, int64_t K);
 
 /* Plain int8 x int8 -> int32 product C[M,N] = A[M,K] * B[N,K]^T (test/diagnostic entry point).
  * igemm_basic_int8_gemm   .../igemm/igemm_BasicInt8Gemm.cu:14-110. */

@@ -27,7 +27,7 @@ def igemm_output_int_quantize_bias_rowcol(X, Wt, bias, biasmax, SXt, SWt, M, N, 
     SO = torch.empty((M // 32, N // 32), dtype=torch.float16, device=dev)
     SXt, SWt = SXt.contiguous(), SWt.contiguous()
     check(lib().jf_igemm_forward(X.data_ptr(), Wt.data_ptr(), SXt.data_ptr(), 1, SXt.stride(0), SWt.data_ptr(), 1, SWt.stride(0),
-                                 M, N, K, 0, O.data_ptr(), SO.data_ptr(), None, _stream()), "igemm_output_int_quantize_bias_rowcol")
+                                 M, N, K, 0, O.data_ptr(), SO.data_ptr(), None, None, 0, _stream()), "igemm_output_int_quantize_bias_rowcol")
     return O, SO
 
 
@@ -39,7 +39,7 @@ def igemm_output_int_quantize_stochastic(X, W, SXt, SW, M, N, K):
     SXt, SW = SXt.contiguous(), SW.contiguous()
     seed, off = rng.next_key()
     check(lib().jf_igemm_dgrad(X.data_ptr(), W.data_ptr(), SXt.data_ptr(), 1, SXt.stride(0), SW.data_ptr(), SW.stride(0), 1,
-                               M, N, K, 0, O.data_ptr(), SO.data_ptr(), None, 1, None, seed, off, _stream()),
+                               M, N, K, 0, O.data_ptr(), SO.data_ptr(), None, 1, None, seed, off, None, 0, _stream()),
           "igemm_output_int_quantize_stochastic")
     return O, SO
 
@@ -52,5 +52,5 @@ def igemm_output_fp_no_quantize(X, W, SXt, SW, M, N, K):
     SXt, SW = SXt.contiguous(), SW.contiguous()
     splits = L.jf_igemm_wgrad_plan(M, N, K, 1)
     check(L.jf_igemm_wgrad(X.data_ptr(), 1, W.data_ptr(), SXt.data_ptr(), SXt.stride(0), 1, SW.data_ptr(), SW.stride(0), 1,
-                           M, N, K, 1, O.data_ptr(), splits, None, _stream()), "igemm_output_fp_no_quantize")
+                           M, N, K, 1, O.data_ptr(), splits, None, None, 0, _stream()), "igemm_output_fp_no_quantize")
     return O

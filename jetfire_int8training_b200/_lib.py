@@ -27,10 +27,12 @@ SIGNATURES = {
     "jf_int8_add": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _int, _vp, _u64, _u64, _vp], _int),
     "jf_int8_add_meanvar": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp], _int),
     "jf_int8_add_meanvar_noalloc": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp], _int),
-    "jf_igemm_forward": ([_vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp], _int),
+    "jf_igemm_forward": ([_vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp], _int),
+    "jf_igemm_op16_bytes": ([_i64, _i64, _i64], _i64),
     "jf_igemm_dgrad": ([_vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _int, _vp,
-                        _u64, _u64, _vp], _int),
-    "jf_igemm_wgrad": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _int, _vp, _vp], _int),
+                        _u64, _u64, _vp, _i64, _vp], _int),
+    "jf_igemm_wgrad": ([_vp, _int, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _int, _vp, _vp, _i64,
+                        _vp], _int),
     "jf_igemm_wgrad_plan": ([_i64, _i64, _i64, _int], _int),
     "jf_igemm_int32": ([_vp, _vp, _i64, _i64, _i64, _vp, _vp], _int),
     "jf_igemm_error_flag": ([], _int),

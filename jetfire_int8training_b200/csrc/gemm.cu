@@ -37,6 +37,7 @@ constexpr int STAGES = 4;
 constexpr int STAGE_BYTES = 128 * 128;          // one operand tile
 constexpr int TMEM_COLS = 512;
 constexpr size_t GEMM_SMEM = 2 * STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr size_t GEMM_SMEM_F16OPS = 2 * 3 * 2 * STAGE_BYTES + 1024 + 256;   // three stages of two boxes per operand
 constexpr long long DRAIN_BUDGET_CLOCKS = 20000000LL;   // ~10 ms: abort-path wait for copies / MMAs already in flight
 constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -96,7 +97,7 @@ __device__ __forceinline__ void drain_wait(uint64_t* bar, uint32_t parity) {
 // a subtraction of 1.5*2^23 instead, for all or for every other pair, measured slower: the add runs on the same pipe.)
 // CONV_INT32 adds the raw integers instead: the plain int32 GEMM behind jf_igemm_int32.
 // ---------------------------------------------------------------------------------------------------------
-enum ConvMode : int { CONV_I2F = 0, CONV_INT32 = 1 };
+enum ConvMode : int { CONV_I2F = 0, CONV_INT32 = 1, CONV_F16OPS = 2 };
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
     uint64_t r;
@@ -122,9 +123,14 @@ __device__ __forceinline__ void scale_accumulate(uint64_t (&acc2)[16], const uin
         return;
     }
     const uint64_t s2 = pack2(s, s);
+    if constexpr (CONV == CONV_F16OPS) {      // the accumulator already holds float(I_p)
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-        acc2[j] = fma2(s2, pack2(__int2float_rn((int)r[2 * j]), __int2float_rn((int)r[2 * j + 1])), acc2[j]);
+        for (int j = 0; j < 16; ++j) acc2[j] = fma2(s2, pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), acc2[j]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            acc2[j] = fma2(s2, pack2(__int2float_rn((int)r[2 * j]), __int2float_rn((int)r[2 * j + 1])), acc2[j]);
+    }
 }
 
 // Re-quantise / convert one 32x32 block held as 32 lanes x 32 values and store it.
@@ -274,6 +280,112 @@ static int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t o
     return JF_OK;
 }
 
+// 2-D fp16 tensor [outer, inner]: box 64 elements (128 B) x 128 rows, 128-byte swizzle, zero fill outside.
+static int make_map_f16(CUtensorMap* map, const void* base, int64_t inner, int64_t outer) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return JF_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    const cuuint64_t strides[1] = {(cuuint64_t)(inner * 2)};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return JF_ERR_LAUNCH;
+    }
+    return JF_OK;
+}
+
+// exact fp16 copy of an int8 tensor (16 elements per thread)
+__global__ void int8_to_f16_kernel(const int8_t* __restrict__ q, int64_t count16, __half* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count16) return;
+    const int4 v = __ldg(reinterpret_cast<const int4*>(q) + i);
+    const uint32_t w[4] = {(uint32_t)v.x ^ 0x80808080u, (uint32_t)v.y ^ 0x80808080u, (uint32_t)v.z ^ 0x80808080u, (uint32_t)v.w ^ 0x80808080u};
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+    uint32_t o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = __byte_perm(w[k], 0x64646464u, 0x5140), hi = __byte_perm(w[k], 0x64646464u, 0x5342);
+        const __half2 a = __hsub2_rn(*reinterpret_cast<const __half2*>(&lo), bias), b = __hsub2_rn(*reinterpret_cast<const __half2*>(&hi), bias);
+        o[2 * k] = *reinterpret_cast<const uint32_t*>(&a); o[2 * k + 1] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out) + 2 * i;
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// exact fp16 copy of the TRANSPOSE of an int8 tensor: q [R, C] row-major -> out [C, R] row-major.  A CTA moves a 128 x 128 tile
+// through shared memory (16-byte chunks XOR-permuted per 16-row group, so that the column reads are bank-conflict free); a thread
+// gathers a 16-row x 4-column patch, transposes it with byte permutes and writes 16 fp16 (32 bytes) of each of 4 output rows:
+// 8 neighbouring threads complete 256 contiguous bytes.
+__global__ void __launch_bounds__(256) int8_to_f16_transposed_kernel(const int8_t* __restrict__ q, int64_t R, int64_t C, __half* __restrict__ out) {
+    __shared__ __align__(16) uint32_t tile[128 * 128 / 4];
+    const int64_t R0 = (int64_t)blockIdx.y * 128, C0 = (int64_t)blockIdx.x * 128;
+    const int t = threadIdx.x;
+    {
+        const int chunk = t & 7;
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int row = (t >> 3) + 32 * pass;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (R0 + row < R && C0 + 16 * chunk < C) v = __ldg(reinterpret_cast<const int4*>(q + (R0 + row) * C + C0 + 16 * chunk));
+            *reinterpret_cast<int4*>(tile + row * 32 + 4 * (chunk ^ ((row >> 4) & 7))) = v;
+        }
+    }
+    __syncthreads();
+    const int warp = t >> 5, lane = t & 31;
+    const int i = lane & 7, cg = 4 * warp + (lane >> 3);
+    if (R0 + 16 * i >= R || C0 + 4 * cg >= C) return;
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+    uint32_t colw[4][4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[k] = tile[(16 * i + 4 * g + k) * 32 + 4 * ((cg >> 2) ^ i) + (cg & 3)];
+        // 4x4 byte transpose: colw[j][g] = rows 4g..4g+3 of column j
+        const uint32_t t0 = __byte_perm(w[0], w[1], 0x5140), t1 = __byte_perm(w[2], w[3], 0x5140);
+        const uint32_t t2 = __byte_perm(w[0], w[1], 0x7362), t3 = __byte_perm(w[2], w[3], 0x7362);
+        colw[0][g] = __byte_perm(t0, t1, 0x5410); colw[1][g] = __byte_perm(t0, t1, 0x7632);
+        colw[2][g] = __byte_perm(t2, t3, 0x5410); colw[3][g] = __byte_perm(t2, t3, 0x7632);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t o[8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint32_t wx = colw[j][g] ^ 0x80808080u;
+            const uint32_t lo = __byte_perm(wx, 0x64646464u, 0x5140), hi = __byte_perm(wx, 0x64646464u, 0x5342);
+            const __half2 a = __hsub2_rn(*reinterpret_cast<const __half2*>(&lo), bias), b = __hsub2_rn(*reinterpret_cast<const __half2*>(&hi), bias);
+            o[2 * g] = *reinterpret_cast<const uint32_t*>(&a); o[2 * g + 1] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + (C0 + 4 * cg + j) * R + R0 + 16 * i);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+// Fill the fp16 operand copies of one GEMM: a16 [M,K] from a ([M,K], or [K,M] when a_transposed), b16 [N,K] likewise.
+static int fill_f16_operands(const int8_t* a, bool a_transposed, const int8_t* b, bool b_transposed, int64_t M, int64_t N, int64_t K,
+                             __half* a16, __half* b16, cudaStream_t st) {
+    auto one = [&](const int8_t* src, bool transposed, int64_t rows, __half* dst) {     // dst [rows, K]
+        if (transposed) {   // src is [K, rows]
+            const dim3 grid((unsigned)((rows + 127) / 128), (unsigned)((K + 127) / 128));
+            int8_to_f16_transposed_kernel<<<grid, 256, 0, st>>>(src, K, rows, dst);
+        } else {
+            const int64_t n16 = rows * K / 16;
+            int8_to_f16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(src, n16, dst);
+        }
+    };
+    if ((K + 127) / 128 > 65535) return JF_ERR_SHAPE;
+    one(a, a_transposed, M, a16);
+    one(b, b_transposed, N, b16);
+    return check_launch();
+}
+
 struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
@@ -317,6 +429,11 @@ static int plan_splits(int64_t M, int64_t N, int64_t K, int split_k, int sm_coun
 
 using namespace jf;
 
+// the fp16-operand path is taken when the caller handed in enough scratch for both operand copies
+static inline bool use_op16(const void* op16, int64_t op16_bytes, int64_t M, int64_t N, int64_t K) {
+    return op16 != nullptr && aligned16(op16) && op16_bytes >= 2 * (M * K + N * K);
+}
+
 static inline int check_gemm_dims(int64_t M, int64_t N, int64_t K) {
     if (!mult32(M) || !mult32(N) || !mult32(K)) return JF_ERR_SHAPE;
     if (M > (1LL << 30) || N > (1LL << 30) || K > (1LL << 30)) return JF_ERR_SHAPE;
@@ -327,7 +444,7 @@ extern "C" {
 
 int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t sx_stride_m, int64_t sx_stride_k, const void* sw,
                      int64_t sw_stride_n, int64_t sw_stride_k, int64_t M, int64_t N, int64_t K, int out_mode, int8_t* y8, void* sy,
-                     void* y16, void* stream) {
+                     void* y16, void* op16, int64_t op16_bytes, void* stream) {
     if (!x || !w || !sx || !sw) return JF_ERR_NULL;
     if (int e = check_gemm_dims(M, N, K)) return e;
     if (!aligned16(x) || !aligned16(w)) return JF_ERR_ALIGN;
@@ -346,12 +463,29 @@ int jf_igemm_forward(const int8_t* x, const int8_t* w, const void* sx, int64_t s
     } else {
         return JF_ERR_ARG;
     }
+    if (use_op16(op16, op16_bytes, M, N, K)) {
+        __half* a16 = (__half*)op16;
+        __half* b16 = a16 + M * K;
+        if (int e = fill_f16_operands(x, false, w, false, M, N, K, a16, b16, (cudaStream_t)stream)) return e;
+        return launch_f16ops(a16, b16, p, (cudaStream_t)stream);
+    }
     return launch_fwd(x, w, p, (cudaStream_t)stream);
+}
+
+/* Bytes of fp16 operand scratch a GEMM with these dimensions needs for the fp16-operand path (2 * (M*K + N*K)), or 0 when that
+ * path is not expected to pay for its conversion passes.  Model: the kernel saves ~20 % of a GEMM that runs at ~630e12 ops/s; the
+ * passes move 3 bytes per operand element at ~5e12 B/s plus two launches. */
+int64_t jf_igemm_op16_bytes(int64_t M, int64_t N, int64_t K) {
+    if (check_gemm_dims(M, N, K)) return 0;
+    const double gain = 0.2 * 2.0 * (double)M * (double)N * (double)K / 630e12;
+    const double cost = 3.0 * ((double)M * K + (double)N * K) / 5e12 + 4e-6;
+    return gain > 1.5 * cost ? 2 * (M * K + N * K) : 0;
 }
 
 int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_stride_m, int64_t sg_stride_k, const void* sw,
                    int64_t sw_stride_k, int64_t sw_stride_n, int64_t M, int64_t N, int64_t K, int out_mode, int8_t* dx8, void* sdx,
-                   void* dx16, int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream) {
+                   void* dx16, int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* op16, int64_t op16_bytes,
+                   void* stream) {
     if (!g || !w || !sg || !sw) return JF_ERR_NULL;
     if (int e = check_gemm_dims(M, N, K)) return e;
     if (!aligned16(g) || !aligned16(w) || (noise && !aligned16(noise))) return JF_ERR_ALIGN;
@@ -371,6 +505,12 @@ int jf_igemm_dgrad(const int8_t* g, const int8_t* w, const void* sg, int64_t sg_
     } else {
         return JF_ERR_ARG;
     }
+    if (use_op16(op16, op16_bytes, M, N, K)) {
+        __half* a16 = (__half*)op16;
+        __half* b16 = a16 + M * K;
+        if (int e = fill_f16_operands(g, false, w, true, M, N, K, a16, b16, (cudaStream_t)stream)) return e;
+        return launch_f16ops(a16, b16, p, (cudaStream_t)stream);
+    }
     return launch_dgrad_layout(g, w, p, (cudaStream_t)stream);
 }
 
@@ -384,7 +524,7 @@ int jf_igemm_wgrad_plan(int64_t M, int64_t N, int64_t K, int split_k) {
 
 int jf_igemm_wgrad(const int8_t* g, int g_transposed, const int8_t* x, const void* sg, int64_t sg_stride_k, int64_t sg_stride_m,
                    const void* sx, int64_t sx_stride_k, int64_t sx_stride_n, int64_t M, int64_t N, int64_t K, int out_dtype, void* dw,
-                   int split_k, float* scratch, void* stream) {
+                   int split_k, float* scratch, void* op16, int64_t op16_bytes, void* stream) {
     if (!g || !x || !sg || !sx || !dw) return JF_ERR_NULL;
     if (int e = check_gemm_dims(M, N, K)) return e;
     if (!aligned16(g) || !aligned16(x) || !aligned16(dw)) return JF_ERR_ALIGN;
@@ -398,15 +538,21 @@ int jf_igemm_wgrad(const int8_t* g, int g_transposed, const int8_t* x, const voi
     p.sa = (const __half*)sg; p.sa_sm = sg_stride_m; p.sa_sk = sg_stride_k;
     p.sb = (const __half*)sx; p.sb_sn = sx_stride_n; p.sb_sk = sx_stride_k;
     cudaStream_t st = (cudaStream_t)stream;
+    const bool f16 = use_op16(op16, op16_bytes, M, N, K);
+    __half* a16 = (__half*)op16;
+    __half* b16 = f16 ? a16 + M * K : nullptr;
+    if (f16)
+        if (int e = fill_f16_operands(g, !g_transposed, x, true, M, N, K, a16, b16, st)) return e;
+    auto launch = [&]() { return f16 ? launch_f16ops(a16, b16, p, st) : (g_transposed ? launch_dgrad_layout(g, x, p, st) : launch_wgrad_layout(g, x, p, st)); };
     if (splits == 1) {
         if (out_dtype == JF_F16) { p.mode = MODE_F16; p.out16 = (__half*)dw; }
         else { p.mode = MODE_F32; p.out32 = (float*)dw; }
-        return g_transposed ? launch_dgrad_layout(g, x, p, st) : launch_wgrad_layout(g, x, p, st);
+        return launch();
     }
     if (!scratch) return JF_ERR_NULL;
     if (!aligned16(scratch)) return JF_ERR_ALIGN;
     p.mode = MODE_F32; p.out32 = scratch;
-    if (int e = g_transposed ? launch_dgrad_layout(g, x, p, st) : launch_wgrad_layout(g, x, p, st)) return e;
+    if (int e = launch()) return e;
     const int64_t count = M * N;
     const unsigned grid = (unsigned)((count / 4 + 255) / 256);
     if (out_dtype == JF_F16) splitk_reduce_kernel<__half><<<grid, 256, 0, st>>>(scratch, splits, count, (__half*)dw);

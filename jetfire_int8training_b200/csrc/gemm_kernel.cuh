@@ -44,26 +44,33 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     constexpr int WARP_TMA = EPI_WARPS, WARP_MMA = EPI_WARPS + 1;   // issuers: WARP_MMA, WARP_MMA + 1
     constexpr bool INT32ACC = (CONV == CONV_INT32);
+    // F16OPS: the operands are fp16 copies of the int8 payloads (exact) and the MMAs are kind::f16 with fp32 accumulation, so
+    // the accumulator already holds float(I_p) (|I_p| < 2^20: every partial sum is an integer below 2^24, exact in fp32) and the
+    // consumers skip the int32 -> fp32 conversion.  A K block is 64 bytes of K instead of 32: a stage holds two 128 x 128 B
+    // boxes per operand (K blocks 0-1 and 2-3) and there are three stages; a K block is two K = 16 MMAs.
+    constexpr bool F16OPS = (CONV == CONV_F16OPS);
+    constexpr int NST = F16OPS ? 3 : STAGES;                            // pipeline stages
+    constexpr int OPER_STAGE = F16OPS ? 2 * STAGE_BYTES : STAGE_BYTES;  // bytes of one operand per stage
     constexpr int NUM_GRP = NUM_ISSUERS, GRP_COLS = 2 * BN;   // two groups of two 128-column accumulators = all 512 TMEM columns
     static_assert(NUM_GRP * GRP_COLS == TMEM_COLS && KB_PER_STAGE == 2 * NUM_GRP, "a stage = one pair of K blocks per group");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + STAGES * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * STAGES * STAGE_BYTES);
+    uint8_t* smem_b = smem + NST * OPER_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * NST * OPER_STAGE);
     uint64_t* full_bar = bars;                            // [STAGES]   TMA -> MMA
-    uint64_t* empty_bar = bars + STAGES;                  // [STAGES]   consumers (int32 mode: MMA) -> TMA
-    uint64_t* grp_full = bars + 2 * STAGES;               // [NUM_GRP]  MMA -> consumers
-    uint64_t* grp_empty = bars + 2 * STAGES + NUM_GRP;    // [NUM_GRP]  consumers -> MMA
-    uint64_t* drain_bar = bars + 2 * STAGES + 2 * NUM_GRP;  // [NUM_ISSUERS]  abort path only: outstanding MMAs of an issuer
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NUM_GRP + NUM_ISSUERS);
+    uint64_t* empty_bar = bars + NST;                  // [STAGES]   consumers (int32 mode: MMA) -> TMA
+    uint64_t* grp_full = bars + 2 * NST;               // [NUM_GRP]  MMA -> consumers
+    uint64_t* grp_empty = bars + 2 * NST + NUM_GRP;    // [NUM_GRP]  consumers -> MMA
+    uint64_t* drain_bar = bars + 2 * NST + 2 * NUM_GRP;  // [NUM_ISSUERS]  abort path only: outstanding MMAs of an issuer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NST + 2 * NUM_GRP + NUM_ISSUERS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < NST; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
         for (int g = 0; g < NUM_GRP; ++g) { ptx::mbar_init(&grp_full[g], 1); ptx::mbar_init(&grp_empty[g], EPI_WARPS); }
         for (int g = 0; g < NUM_ISSUERS; ++g) ptx::mbar_init(&drain_bar[g], 1);
         *abort_flag = 0;
@@ -97,10 +104,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const int64_t kb0 = split * p.kb_per_split;
                 const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
                 for (int64_t kb = kb0; kb < kb1; kb += KB_PER_STAGE, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    const uint32_t s = it % NST, ph = (it / NST) & 1u;
                     if (!(ok = bounded_wait<true>(&empty_bar[s], ph ^ 1u, abort_flag, 1))) break;
-                    ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * OPER_STAGE);
                     const int32_t k_off = (int32_t)(kb * QB);
+                    if (F16OPS) {
+                        // K-major fp16 operands: two boxes of 64 elements of K each (the second one may lie past K: zero fill)
+                        ptx::tma_load_2d(smem_a + s * OPER_STAGE, &map_a, &full_bar[s], k_off, (int32_t)(tm * BM));
+                        ptx::tma_load_2d(smem_a + s * OPER_STAGE + STAGE_BYTES, &map_a, &full_bar[s], k_off + 64, (int32_t)(tm * BM));
+                        ptx::tma_load_2d(smem_b + s * OPER_STAGE, &map_b, &full_bar[s], k_off, (int32_t)(tn * BN));
+                        ptx::tma_load_2d(smem_b + s * OPER_STAGE + STAGE_BYTES, &map_b, &full_bar[s], k_off + 64, (int32_t)(tn * BN));
+                        continue;
+                    }
                     if (A_MN) ptx::tma_load_2d(smem_a + s * STAGE_BYTES, &map_a, &full_bar[s], (int32_t)(tm * BM), k_off);
                     else      ptx::tma_load_2d(smem_a + s * STAGE_BYTES, &map_a, &full_bar[s], k_off, (int32_t)(tm * BM));
                     if (B_MN) ptx::tma_load_2d(smem_b + s * STAGE_BYTES, &map_b, &full_bar[s], (int32_t)(tn * BN), k_off);
@@ -109,7 +124,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             if (*abort_flag) {
                 // abort: the copies of the last (up to STAGES) armed stages may still be landing in this CTA's shared memory
-                for (uint32_t j = it > STAGES ? it - STAGES : 0u; j < it; ++j) drain_wait(&full_bar[j % STAGES], (j / STAGES) & 1u);
+                for (uint32_t j = it > NST ? it - NST : 0u; j < it; ++j) drain_wait(&full_bar[j % NST], (j / NST) & 1u);
             }
         }
     } else if (warp >= WARP_MMA) {
@@ -124,15 +139,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const int64_t kb0 = split * p.kb_per_split;
                 const int64_t kb1 = min(p.nkb, kb0 + p.kb_per_split);
                 for (int64_t kb = kb0; kb < kb1 && ok; kb += KB_PER_STAGE, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    const uint32_t s = it % NST, ph = (it / NST) & 1u;
                     const int nblk = (int)min((int64_t)KB_PER_STAGE, kb1 - kb);
                     if (!INT32ACC && nblk <= 2 * (int)w) continue;   // the stage holds no K block of this issuer's pair
                     if (!(ok = bounded_wait<true>(&full_bar[s], ph, abort_flag, 2))) break;
                     ptx::tc_fence_after();
                     // descriptors of K block 0 of the stage; K block j is 32 bytes further along a K-major row and 32 K-rows
                     // (4096 B) further in an MN-major tile, i.e. +2 / +256 in the descriptor's 16-byte address units
-                    const uint64_t da0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem_a + s * STAGE_BYTES), A_MN ? 128 * 128 : 16, 1024);
-                    const uint64_t db0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem_b + s * STAGE_BYTES), B_MN ? 128 * 128 : 16, 1024);
+                    const uint64_t da0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem_a + s * OPER_STAGE), A_MN ? 128 * 128 : 16, 1024);
+                    const uint64_t db0 = ptx::make_smem_desc_sw128(ptx::smem_u32(smem_b + s * OPER_STAGE), B_MN ? 128 * 128 : 16, 1024);
                     if (INT32ACC) {
                         // diagnostic mode: one issuer; the tensor core accumulates the whole K range of a tile in one accumulator
                         const uint32_t g = gi % NUM_GRP;
@@ -153,6 +168,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         const int npair = min(2, nblk - 2 * (int)w);
                         for (int jj = 0; jj < npair; ++jj) {
                             const int j = 2 * (int)w + jj;
+                            if (F16OPS) {
+                                // issuer w's pair lives in box w of the stage; K block jj of the pair starts 64 B into the 128-byte
+                                // swizzle row, its two K = 16 halves are 32 B apart (descriptor address units of 16 B)
+                                constexpr uint32_t idesc16 = ptx::make_idesc_f16(BM, BN);
+                                const uint64_t off = (uint64_t)(w * (STAGE_BYTES / 16) + jj * 4);
+                                ptx::umma_f16(tmem_base + w * GRP_COLS + jj * BN, da0 + off, db0 + off, idesc16, 0u);
+                                ptx::umma_f16(tmem_base + w * GRP_COLS + jj * BN, da0 + off + 2, db0 + off + 2, idesc16, 1u);
+                                continue;
+                            }
                             ptx::umma_i8(tmem_base + w * GRP_COLS + jj * BN, da0 + (uint64_t)(A_MN ? j * 256 : j * 2),
                                          db0 + (uint64_t)(B_MN ? j * 256 : j * 2), idesc, 0u);
                         }
@@ -240,7 +264,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (!INT32ACC && stage_end) {
                     // the last pair of a shared-memory stage has completed (the earlier pair was seen before): hand the stage
                     // back to the TMA producer
-                    if (warp == 0 && lane == 0) ptx::mbar_arrive(&empty_bar[sit % STAGES]);
+                    if (warp == 0 && lane == 0) ptx::mbar_arrive(&empty_bar[sit % NST]);
                     ++sit;
                 }
                 accumulate(r, two ? s1 : s0);

@@ -1,6 +1,8 @@
 """GPU parity of the per-block INT8 GEMMs (tcgen05 kernels, through the ctypes C ABI) against the CPU oracle.
 Everything here is integer / exactly-specified fp32 work, so the bar is bit-exact: int32 block products, int8 payloads,
-fp16 scales, fp16 dense outputs -- for round-to-nearest and, with a fixed Philox key, for stochastic rounding."""
+fp16 scales, fp16 dense outputs -- for round-to-nearest and, with a fixed Philox key, for stochastic rounding.
+Every forward / backward / split-K case runs on BOTH GEMM paths: the int8-operand kernel (kind::i8 + conversion in the
+consumers) and the fp16-operand kernel (conversion passes + kind::f16), which the library picks by size in production."""
 import numpy as np
 import pytest
 import torch
@@ -21,6 +23,12 @@ def LIN():
 def L():
     from jetfire_int8training_b200._lib import lib
     return lib()
+
+
+@pytest.fixture(params=[False, True], ids=["i8ops", "f16ops"])
+def op16(request):
+    """operand_scratch argument of the Linear wrappers: False = int8-operand kernel, True = fp16-operand kernel."""
+    return request.param
 
 
 @pytest.fixture(autouse=True)
@@ -70,17 +78,17 @@ FWD_SHAPES = [(128, 128, 32), (128, 128, 256), (32, 64, 96), (160, 288, 416), (5
 
 
 @pytest.mark.parametrize("M,N,K", FWD_SHAPES)
-def test_forward_bit_exact(LIN, oracle, M, N, K):
+def test_forward_bit_exact(LIN, oracle, op16, M, N, K):
     A, B, SA, SB = rand_operands(M + N + K, M, N, K)
-    q, s = LIN.int8_linear_forward(t(A), t(SA), t(B), t(SB), True, 32)
+    q, s = LIN.int8_linear_forward(t(A), t(SA), t(B), t(SB), True, 32, operand_scratch=op16)
     qo, so, do = oracle.linear_forward(A, SA, B, SB, dequantized=True)
     assert_bits_equal(n(q), qo, "payload"); assert_bits_equal(n(s), so, "scales")
-    y16 = LIN.int8_linear_forward(t(A), t(SA), t(B), t(SB), False, 32)
+    y16 = LIN.int8_linear_forward(t(A), t(SA), t(B), t(SB), False, 32, operand_scratch=op16)
     assert_bits_equal(n(y16), do, "dequantised fp16")
 
 
 @pytest.mark.parametrize("M,N,K", FWD_SHAPES)
-def test_backward_bit_exact(LIN, oracle, M, N, K):
+def test_backward_bit_exact(LIN, oracle, op16, M, N, K):
     """dgrad (M x Cin x Cout) with a fixed Philox key and wgrad (Cout x Cin x tokens), operands in their natural layouts."""
     tokens, Cin, Cout = M, N, K
     rng = np.random.default_rng(tokens + Cin * 3 + Cout)
@@ -92,22 +100,23 @@ def test_backward_bit_exact(LIN, oracle, M, N, K):
     SW = rng.uniform(1e-3, 1e-1, (Cout // 32, Cin // 32)).astype(np.float16)
     key = (0xC0FFEE, 3)
     gx, gs, gw = LIN.int8_linear_backward(t(X), t(SX), t(G), t(SG), None, t(W), t(SW), 32, stochastic=True, sr_key=key,
-                                          wgrad_split_k=1)
+                                          wgrad_split_k=1, operand_scratch=op16)
     noise = oracle.sr_noise(tokens, Cin, *key)
     qo, so = oracle.linear_dgrad(G, SG, W, SW, noise)
     assert_bits_equal(n(gx), qo, "dgrad payload"); assert_bits_equal(n(gs), so, "dgrad scales")
     assert_bits_equal(n(gw), oracle.linear_wgrad(G, SG, X, SX), "wgrad fp16")
     # round-to-nearest and dequantised variants
-    gx, gs, _ = LIN.int8_linear_backward(t(X), t(SX), t(G), t(SG), None, t(W), t(SW), 32, stochastic=False, wgrad_split_k=1)
+    gx, gs, _ = LIN.int8_linear_backward(t(X), t(SX), t(G), t(SG), None, t(W), t(SW), 32, stochastic=False, wgrad_split_k=1,
+                                         operand_scratch=op16)
     qo, so, do = oracle.linear_dgrad(G, SG, W, SW, None, dequantized=True)
     assert_bits_equal(n(gx), qo, "dgrad RN payload"); assert_bits_equal(n(gs), so, "dgrad RN scales")
     g16, _ = LIN.int8_linear_backward(t(X), t(SX), t(G), t(SG), None, t(W), t(SW), 32, stochastic=False, dgrad_quantize=False,
-                                      wgrad_split_k=1)
+                                      wgrad_split_k=1, operand_scratch=op16)
     assert_bits_equal(n(g16), do, "dgrad dequantised")
 
 
 @pytest.mark.parametrize("tokens,Cin,Cout,split", [(2048, 128, 128, 4), (4096, 768, 768, 0), (1024, 96, 160, 3)])
-def test_wgrad_split_k_is_deterministic_and_matches_oracle(LIN, L, oracle, tokens, Cin, Cout, split):
+def test_wgrad_split_k_is_deterministic_and_matches_oracle(LIN, L, oracle, op16, tokens, Cin, Cout, split):
     rng = np.random.default_rng(tokens + split)
     G = rng.integers(-127, 128, (tokens, Cout), dtype=np.int8)
     X = rng.integers(-127, 128, (tokens, Cin), dtype=np.int8)
@@ -116,7 +125,7 @@ def test_wgrad_split_k_is_deterministic_and_matches_oracle(LIN, L, oracle, token
     eff = L.jf_igemm_wgrad_plan(Cout, Cin, tokens, split)
     assert eff >= 1
     for dt, ndt in ((torch.float32, np.float32), (torch.float16, np.float16)):
-        dw = LIN.int8_linear_wgrad(t(X), t(SX), t(G), t(SG), dt, split)
+        dw = LIN.int8_linear_wgrad(t(X), t(SX), t(G), t(SG), dt, split, operand_scratch=op16)
         want = oracle.linear_wgrad(G, SG, X, SX, split_k=eff, out_dtype=ndt)
         assert_bits_equal(n(dw), want, f"wgrad split {eff} {ndt.__name__}")
         assert torch.equal(dw, LIN.int8_linear_wgrad(t(X), t(SX), t(G), t(SG), dt, split))
@@ -191,7 +200,7 @@ def test_full_size_properties(LIN, L):
     q3 = torch.empty_like(q); s3 = torch.empty_like(s)
     SBt = SB.t().contiguous()
     rc = L.jf_igemm_dgrad(A.data_ptr(), Bt.data_ptr(), SA.data_ptr(), SA.stride(0), SA.stride(1), SBt.data_ptr(), SBt.stride(0),
-                          SBt.stride(1), M, N, K, 0, q3.data_ptr(), s3.data_ptr(), None, 0, None, 0, 0, st)
+                          SBt.stride(1), M, N, K, 0, q3.data_ptr(), s3.data_ptr(), None, 0, None, 0, 0, None, 0, st)
     assert rc == 0
     assert torch.equal(q, q3) and torch.equal(s, s3)
     # a 512-row slab against the exact integer product with unit scales
@@ -208,8 +217,8 @@ def test_errors(L):
     a = torch.zeros((64, 64), dtype=torch.int8, device=DEV)
     s = torch.ones((2, 2), dtype=torch.float16, device=DEV)
     assert L.jf_igemm_forward(a.data_ptr(), a.data_ptr(), s.data_ptr(), 2, 1, s.data_ptr(), 2, 1, 64, 48, 64, 0, a.data_ptr(),
-                              s.data_ptr(), None, st) == -2                       # N not a multiple of 32
+                              s.data_ptr(), None, None, 0, st) == -2              # N not a multiple of 32
     assert L.jf_igemm_forward(None, a.data_ptr(), s.data_ptr(), 2, 1, s.data_ptr(), 2, 1, 64, 64, 64, 0, a.data_ptr(),
-                              s.data_ptr(), None, st) == -1                       # NULL operand
+                              s.data_ptr(), None, None, 0, st) == -1              # NULL operand
     assert L.jf_igemm_forward(a.data_ptr() + 1, a.data_ptr(), s.data_ptr(), 2, 1, s.data_ptr(), 2, 1, 64, 64, 64, 0,
-                              a.data_ptr(), s.data_ptr(), None, st) == -3         # misaligned operand
+                              a.data_ptr(), s.data_ptr(), None, None, 0, st) == -3   # misaligned operand
