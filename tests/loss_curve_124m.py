@@ -3,13 +3,15 @@ on the reference's INT8 recipe restated in plain torch (tests/torch_recipe.py, p
 kernels by tests/test_recipe_golden.py) -- same initial weights, same batches, same optimiser; only the stochastic-rounding noise
 streams differ.
 
-    python tests/loss_curve_124m.py [--steps 2000] [--micro-batch 12] [--layers 12] [--stream learnable|uniform]
+    python tests/loss_curve_124m.py [--steps 2000] [--micro-batch 12] [--layers 12] [--stream learnable|uniform] [--seed-variance]
 
 GPT-2 124M: 12 layers, 12 heads, d = 768, context 1024, vocabulary 50304, AdamW lr 6e-4 (100 warm-up steps), betas (0.9, 0.95),
 weight decay 0.1, gradient clipping 1.0.  Token stream: seeded synthetic ids.  `uniform` draws them uniformly (nothing can be
 learnt: the curve stays at ln 50304); `learnable` (default) makes the next token (5 t + 17 + {0,1,2}) mod 50304, so the loss
 falls and a mismatch between the two implementations would show.  Prints one JSON line with the mean loss of every 100-step
-window for both runs and the largest relative gap between them.
+window for both runs and the largest relative gap between them.  --seed-variance runs the CUDA operators twice instead, with
+two different stochastic-rounding seeds and everything else equal: the gap between those two curves is the run-to-run spread of
+ONE implementation, the yardstick for the gap between two implementations (it is largest where the loss falls fastest).
 """
 import argparse
 import contextlib
@@ -87,6 +89,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=12)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--stream", default="learnable", choices=["learnable", "uniform"])
+    ap.add_argument("--seed-variance", action="store_true")
     args = ap.parse_args()
     from jetfire_int8training_b200 import rng
     from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
@@ -99,12 +102,17 @@ def main():
     del ours
     torch.cuda.empty_cache()
     torch.manual_seed(1)
-    b = train(theirs, args, use_recipe=True)
+    if args.seed_variance:
+        rng.manual_seed(12345)                       # a different stochastic-rounding stream, same weights and batches
+        b = train(theirs, args, use_recipe=False)
+    else:
+        b = train(theirs, args, use_recipe=True)
     w = 100
     wins = [(round(float(a[i:i + w].mean()), 4), round(float(b[i:i + w].mean()), 4)) for i in range(0, args.steps - w + 1, w)]
     gap = max(abs(x - y) / y for x, y in wins)
     print(json.dumps({"model": f"GPT-2 124M shape, {args.layers} layers", "steps": args.steps, "micro_batch": args.micro_batch, "stream": args.stream,
-                      "window": w, "window_means_cuda_vs_recipe": wins, "max_relative_gap_of_window_means": gap,
+                      "window": w, "compared": "cuda (SR seed 0) vs cuda (SR seed 12345)" if args.seed_variance else "cuda vs recipe",
+                      "window_means_cuda_vs_recipe": wins, "max_relative_gap_of_window_means": gap,
                       "first_loss": [float(a[0]), float(b[0])], "last_window": wins[-1], "finite": bool(torch.isfinite(a).all() and torch.isfinite(b).all())}))
 
 
