@@ -55,6 +55,13 @@ int jf_abi_version(void);
 int jf_int8_quantize(const void* x, int x_dtype, int64_t M, int64_t N, int8_t* q, void* s, int8_t* qt,
                      int stochastic, const float* noise, uint64_t seed, uint64_t offset, void* stream);
 
+/* The same round-to-nearest quantisation for up to 8 tensors of one dtype in one launch: x[j] is [M[j], N[j]], q[j] / s[j] its payload
+ * and scales.  For the weight matrices a caller quantises at the start of every forward pass (INT8_GPT2/qmodel.py:92, 139, 199-200:
+ * four int8_quantize calls per transformer block); results are identical to `count` calls of jf_int8_quantize.  `x`, `M`, `N`, `q`, `s`
+ * are host arrays of length `count` (1..8); they are copied into the kernel parameters. */
+int jf_int8_quantize_multi(int count, const void* const* x, int x_dtype, const int64_t* M, const int64_t* N, int8_t* const* q,
+                           void* const* s, void* stream);
+
 /* int8_dequantize(x, s_x, QB)                 Jetfire/Nonlinear/dequantize.py:86-116 (kernel :28-84)
  * y: fp32 [M,N] = fp32(fp16(q) * s)  (the product is rounded to fp16 first, as the reference does). */
 int jf_int8_dequantize(const int8_t* q, const void* s, int64_t M, int64_t N, float* y, void* stream);

@@ -15,7 +15,7 @@ from .. import rng
 from .._lib import lib, check
 
 __all__ = [
-    "int8_quantize", "int8_quantize_transpose", "int8_transpose", "int8_dequantize",
+    "int8_quantize", "int8_quantize_many", "int8_quantize_transpose", "int8_transpose", "int8_dequantize",
     "int8_gelu_forward", "int8_gelu_backward", "int8_layernorm_forward", "int8_layernorm_backward",
     "int8_add_Ifp_Ig16_Ofp_Og", "int8_add_Ifp_Ig16_Ofp_Og_MeanVar",
 ]
@@ -81,6 +81,30 @@ def int8_quantize(x, QB, stochastic=False, *, noise=None, sr_key=None):
     check(lib().jf_int8_quantize(x2.data_ptr(), _DTYPE[x2.dtype], M, N, q.data_ptr(), s.data_ptr(), None, st, nz, seed, off,
                                  _stream()), "int8_quantize")
     return _unflat(q, bs), _unflat(s, bs)
+
+
+def int8_quantize_many(tensors, QB):
+    """Round-to-nearest int8_quantize of several 2-D tensors (same dtype and device) with one kernel launch per 8 tensors: the
+    weight matrices that the reference quantises one by one at the start of every forward pass (INT8_GPT2/qmodel.py:92, 139,
+    199-200).  Returns [(q, scale), ...], bit-identical to int8_quantize on each tensor."""
+    import ctypes
+    _qb(QB)
+    tensors = [t if t.dtype in _DTYPE else t.float() for t in tensors]
+    _need_cuda(*tensors)
+    assert all(t.dim() == 2 and t.dtype == tensors[0].dtype and t.device == tensors[0].device for t in tensors)
+    tensors = [t.contiguous() for t in tensors]
+    outs = []
+    for i in range(0, len(tensors), 8):
+        grp = tensors[i:i + 8]
+        n = len(grp)
+        qs = [torch.empty(t.shape, dtype=torch.int8, device=t.device) for t in grp]
+        ss = [torch.empty((t.shape[0] // 32, t.shape[1] // 32), dtype=torch.float16, device=t.device) for t in grp]
+        vp, i64 = ctypes.c_void_p * n, ctypes.c_int64 * n
+        check(lib().jf_int8_quantize_multi(n, vp(*[t.data_ptr() for t in grp]), _DTYPE[grp[0].dtype], i64(*[t.shape[0] for t in grp]),
+                                           i64(*[t.shape[1] for t in grp]), vp(*[q.data_ptr() for q in qs]),
+                                           vp(*[s.data_ptr() for s in ss]), _stream()), "int8_quantize_many")
+        outs += list(zip(qs, ss))
+    return outs
 
 
 def int8_quantize_transpose(x, QB, stochastic=False, transpose_output_2d=False, *, noise=None, sr_key=None):

@@ -17,6 +17,7 @@ SIGNATURES = {
     "jf_last_cuda_error": ([], _int),
     "jf_abi_version": ([], _int),
     "jf_int8_quantize": ([_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp, _u64, _u64, _vp], _int),
+    "jf_int8_quantize_multi": ([_int, _vp, _int, _vp, _vp, _vp, _vp, _vp], _int),
     "jf_int8_dequantize": ([_vp, _vp, _i64, _i64, _vp, _vp], _int),
     "jf_int8_transpose": ([_vp, _i64, _i64, _vp, _vp], _int),
     "jf_int8_gelu_forward": ([_vp, _vp, _i64, _i64, _vp, _vp, _vp], _int),

@@ -1003,6 +1003,50 @@ quantize4_kernel(const T* __restrict__ x, int64_t M, int64_t N, int8_t* __restri
     }
 }
 
+// Round-to-nearest quantisation of up to 8 tensors of one dtype in ONE launch (the weight matrices of a transformer block, or of
+// several blocks): the blocks of all tensors are numbered consecutively and a warp finds its tensor by comparing its block number
+// with the running totals.  One block per warp per iteration, no prefetch (the tensors are small and many).
+constexpr int QMULTI_MAX = 8;
+struct QuantizeJobs {
+    const void* x[QMULTI_MAX];
+    int8_t* q[QMULTI_MAX];
+    __half* s[QMULTI_MAX];
+    int64_t N[QMULTI_MAX];             // columns
+    int64_t first_block[QMULTI_MAX + 1];   // first global block number of tensor j; [count] = total
+    int count;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 3) quantize_multi_kernel(const QuantizeJobs jobs) {
+    const int64_t total = jobs.first_block[jobs.count];
+    const int64_t stride = (int64_t)gridDim.x * WARPS;
+    const int lane = threadIdx.x & 31, r = lane >> 3, c = lane & 7;
+    using Raw = typename std::conditional<sizeof(T) == 4, float4, uint2>::type;
+    SrCfg sr{};
+    for (int64_t g = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); g < total; g += stride) {
+        int j = 0;
+#pragma unroll
+        for (int k = 1; k < QMULTI_MAX; ++k) j += (k < jobs.count && g >= jobs.first_block[k]) ? 1 : 0;
+        const int64_t blk = g - jobs.first_block[j];
+        const int64_t N = jobs.N[j], blocks_n = N / QB;
+        const int64_t tm = (int64_t)((uint32_t)blk / (uint32_t)blocks_n), tn = (int64_t)((uint32_t)blk % (uint32_t)blocks_n);
+        const int64_t base = (tm * QB + r) * N + tn * QB + 4 * c;
+        const T* x = static_cast<const T*>(jobs.x[j]);
+        Raw cur[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[i] = __ldg(reinterpret_cast<const Raw*>(x + base + (int64_t)(4 * i) * N));
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 w = widen4(cur[i], T());
+            m = fmaxf(fmaxf(m, fmaxf(fabsf(w.x), fabsf(w.y))), fmaxf(fabsf(w.z), fabsf(w.w)));
+        }
+        const float scale32 = __fdiv_rn(__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m))), 127.0f);
+        emit_block4<false, false>([&](int i) { return widen4(cur[i], T()); }, scale32, base, N, c, jobs.q[j], sr);
+        if (lane == 0) jobs.s[j][blk] = __float2half_rn(scale32);
+    }
+}
+
 // =========================================================================================================
 // residual add (+ optional row statistics): y = x1 + q2*s2 (fp32); store y; block quantise y by truncation
 // =========================================================================================================
@@ -1241,6 +1285,36 @@ int jf_int8_quantize(const void* x, int x_dtype, int64_t M, int64_t N, int8_t* q
         case JF_F32: launch_quantize<float>(x, M, N, q, sh, qt, sto, sr, st); break;
         case JF_F16: launch_quantize<__half>(x, M, N, q, sh, qt, sto, sr, st); break;
         case JF_BF16: launch_quantize<__nv_bfloat16>(x, M, N, q, sh, qt, sto, sr, st); break;
+        default: return JF_ERR_DTYPE;
+    }
+    return check_launch();
+}
+
+int jf_int8_quantize_multi(int count, const void* const* x, int x_dtype, const int64_t* M, const int64_t* N, int8_t* const* q,
+                           void* const* s, void* stream) {
+    if (count <= 0 || count > QMULTI_MAX) return JF_ERR_ARG;
+    JF_REQUIRE_PTR(x); JF_REQUIRE_PTR(M); JF_REQUIRE_PTR(N); JF_REQUIRE_PTR(q); JF_REQUIRE_PTR(s);
+    QuantizeJobs jobs{};
+    jobs.count = count;
+    int64_t total = 0;
+    for (int j = 0; j < count; ++j) {
+        JF_REQUIRE_PTR(x[j]); JF_REQUIRE_PTR(q[j]); JF_REQUIRE_PTR(s[j]);
+        if (int e = check_mn(M[j], N[j])) return e;
+        JF_REQUIRE_ALIGNED(x[j]); JF_REQUIRE_ALIGNED(q[j]);
+        jobs.x[j] = x[j]; jobs.q[j] = q[j]; jobs.s[j] = (__half*)s[j]; jobs.N[j] = N[j];
+        jobs.first_block[j] = total;
+        total += (M[j] / QB) * (N[j] / QB);
+    }
+    jobs.first_block[count] = total;
+    if (total >= (int64_t(1) << 31)) return JF_ERR_SHAPE;
+    const int64_t ctas = (total + WARPS - 1) / WARPS;
+    const int cap = persistent_ctas(3) * 4;
+    const unsigned grid = (unsigned)(ctas > cap ? cap : ctas);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case JF_F32: quantize_multi_kernel<float><<<grid, THREADS, 0, st>>>(jobs); break;
+        case JF_F16: quantize_multi_kernel<__half><<<grid, THREADS, 0, st>>>(jobs); break;
+        case JF_BF16: quantize_multi_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(jobs); break;
         default: return JF_ERR_DTYPE;
     }
     return check_launch();

@@ -156,6 +156,22 @@ def test_quantize_vs_oracle(NL, oracle, M, N, dt):
     assert_bits_equal(n(NL.int8_dequantize(q2, s2, 32)), oracle.int8_dequantize(qo, so), "dequantize")
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
+def test_quantize_many_equals_one_by_one(NL, oracle, dt):
+    """Eleven ragged tensors (two launches: 8 + 3) against the oracle and against int8_quantize on each."""
+    shapes = SHAPES + [(2304, 768), (768, 3072), (32, 4096), (160, 64), (3072, 96), (64, 64)]
+    g = torch.Generator().manual_seed(11)
+    xs = [outlier_randn(g, M, N).to(dt) for M, N in shapes]
+    xs[3][32:64, 64:96] = 0
+    outs = NL.int8_quantize_many([x.to(DEV) for x in xs], 32)
+    assert len(outs) == len(xs)
+    for x, (q, s) in zip(xs, outs):
+        qo, so = oracle.int8_quantize(x.float().numpy())
+        assert_bits_equal(n(q), qo, "q"); assert_bits_equal(n(s), so, "s")
+        q1, s1 = NL.int8_quantize(x.to(DEV), 32)
+        assert torch.equal(q, q1) and torch.equal(s, s1)
+
+
 @pytest.mark.parametrize("M,N", [(64, 160), (256, 768)])
 def test_quantize_philox_bit_exact_and_unbiased(NL, oracle, M, N):
     g = torch.Generator().manual_seed(5)

@@ -132,10 +132,11 @@ def int8_add_Ifp_Ig16_Ofp_Og_MeanVar(x1, x2, s_x2, B):
 def int8_linear_forward(X8_3D, SX16_3D, W8, SW16, output_quantized, B):
     x2, bs = _flat(X8_3D); sx2, _ = _flat(SX16_3D)
     y = (_deq(x2, sx2).double() @ _deq(W8, SW16).double().t()).float()      # linear_fwd.py:4-32
+    q, s = _quant(y, False)
     if output_quantized:
-        q, s = _quant(y, False)
         return _unflat(q, bs), _unflat(s, bs)
-    return _unflat(y.half(), bs)
+    # linear_fwd.py:30: the quantised output is dequantised again (int8 * fp16 scale, a product in fp16), not the raw accumulator
+    return _unflat(_deq(q, s, half_product=True).half(), bs)
 
 
 def int8_linear_backward(X8_3D, SX16_3D, G8_3D, SG16_3D, G8T, W8, SW16, B, stochastic=True, dgrad_quantize=True, *,
@@ -144,7 +145,7 @@ def int8_linear_backward(X8_3D, SX16_3D, G8_3D, SG16_3D, G8T, W8, SW16, B, stoch
     gd, xd, wd = _deq(g2, sg2).double(), _deq(x2, sx2).double(), _deq(W8, SW16).double()
     gx = (gd @ wd).float()                                               # linear_bwd.py:17
     gw = (gd.t() @ xd).float().to(wgrad_out_dtype)                       # linear_bwd.py:19
+    q, s = _quant(gx, True)                                              # the reference's dgrad kernel always rounds stochastically
     if dgrad_quantize:
-        q, s = _quant(gx, stochastic)
         return _unflat(q, bs), _unflat(s, bs), gw
-    return _unflat(gx.half(), bs), gw
+    return _unflat(_deq(q, s, half_product=True).half(), bs), gw         # linear_bwd.py:27: dequantised again, fp16 product
