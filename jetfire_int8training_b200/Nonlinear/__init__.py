@@ -8,6 +8,11 @@ current stream; QB must be 32.
 
 Extras not in the reference (keyword-only): `noise=` feeds an explicit fp32 noise tensor to a stochastic operator
 (used to reproduce the reference's rounding bit for bit), `sr_key=(seed, offset)` pins the Philox key of one call.
+`set_sr_noise("torch")` makes every stochastic operator draw its noise the way the reference does -- one fp32 tensor
+`uniform_(-0.5, 0.5)` per call from torch's CUDA generator (Jetfire/Nonlinear/quantize.py:143-144, gelu_bwd.py:192,
+layernorm.py:493, add.py:185) -- so that a run seeded with `torch.manual_seed` rounds exactly like the reference run with the
+same seed, at the price of writing and reading 4 bytes of noise per element; the default "philox" generates 16 noise bits per
+element inside the kernel.
 """
 import torch
 
@@ -17,11 +22,21 @@ from .._lib import lib, check
 __all__ = [
     "int8_quantize", "int8_quantize_many", "int8_quantize_transpose", "int8_transpose", "int8_dequantize",
     "int8_gelu_forward", "int8_gelu_backward", "int8_layernorm_forward", "int8_layernorm_backward",
-    "int8_add_Ifp_Ig16_Ofp_Og", "int8_add_Ifp_Ig16_Ofp_Og_MeanVar",
+    "int8_add_Ifp_Ig16_Ofp_Og", "int8_add_Ifp_Ig16_Ofp_Og_MeanVar", "set_sr_noise",
 ]
 
 _DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 TILE_N = 128
+_SR_NOISE = "philox"
+
+
+def set_sr_noise(mode):
+    """"philox": in-kernel Philox4x32-10 keyed by rng.next_key() (default).  "torch": the reference's noise stream."""
+    global _SR_NOISE
+    if mode not in ("philox", "torch"):
+        raise ValueError("sr noise mode is 'philox' or 'torch'")
+    previous, _SR_NOISE = _SR_NOISE, mode
+    return previous
 
 
 def _stream():
@@ -59,6 +74,9 @@ def _sr_args(stochastic, noise, sr_key, like):
         return 0, None, 0, 0, None
     if noise is not None:
         noise = noise.reshape(like.shape).to(device=like.device, dtype=torch.float32).contiguous()
+        return 1, noise.data_ptr(), 0, 0, noise
+    if sr_key is None and _SR_NOISE == "torch":
+        noise = torch.empty(like.shape, dtype=torch.float32, device=like.device).uniform_(-0.5, 0.5)
         return 1, noise.data_ptr(), 0, 0, noise
     seed, offset = sr_key if sr_key is not None else rng.next_key()
     return 1, None, seed, offset, None

@@ -97,6 +97,35 @@ __device__ __forceinline__ Divisor make_divisor(float b) {
 }
 // use: q0 = a * d.inv;  q = fma(fma(-d.b, q0, a), d.inv, q0)   (d.fast)      or      q = a / d.b   (otherwise)
 
+// Two fp32 values in one 64-bit register and the two-wide IEEE operations on them (each half is rounded exactly like the scalar
+// mul.rn / add.rn / fma.rn; subnormals are kept): one issue slot for two elements in the kernels that are bound by instruction issue.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// the exact quotients a / d.b of two values (d.fast)
+__device__ __forceinline__ uint64_t f2_div_fast(uint64_t a2, uint64_t inv2, uint64_t negb2) {
+    const uint64_t q0 = f2_mul(a2, inv2);
+    return f2_fma(f2_fma(negb2, q0, a2), inv2, q0);
+}
+
 // fp16 product of an int8 payload value and its fp16 scale, as the reference's "int8 * fp16" does
 // (the int8 is converted to fp16 exactly, the product is rounded to fp16 once).  q*s is exact in fp32.
 __device__ __forceinline__ __half deq16(int q, float s_as_float) { return __float2half_rn(__fmul_rn((float)q, s_as_float)); }

@@ -187,6 +187,7 @@ __device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const
     // One decision per warp: the Markstein path is exact only inside its exponent window.  The two paths are separate
     // instantiations of the loop (a run-time flag inside the element loop keeps both alive for every element).
     const bool fast = __all_sync(0xffffffffu, d.fast || zero);
+    const uint64_t inv2 = f2_pack(d.inv, d.inv), negb2 = f2_pack(-d.b, -d.b), magic2 = f2_pack(12582912.0f, 12582912.0f);
     auto rows = [&](auto fast_c) {
     constexpr bool FAST = decltype(fast_c)::value;
 #pragma unroll
@@ -214,20 +215,26 @@ __device__ __forceinline__ void emit_quantized(RowF&& rowf, float scale32, const
             for (int k = 0; k < 4; ++k) {
                 uint32_t b[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float a = av[4 * k + j];
-                    float x;
+                for (int j = 0; j < 4; j += 2) {
+                    float x0, x1;
                     if (FAST) {
-                        const float q0 = __fmul_rn(a, d.inv);
-                        x = __fmaf_rn(__fmaf_rn(-d.b, q0, a), d.inv, q0);
+                        const uint64_t x2 = f2_div_fast(f2_pack(av[4 * k + j], av[4 * k + j + 1]), inv2, negb2);
+                        if (!SR && !TRUNC) {
+                            f2_unpack(f2_add(x2, magic2), x0, x1);
+                            b[j] = __float_as_uint(x0); b[j + 1] = __float_as_uint(x1);
+                            continue;
+                        }
+                        f2_unpack(x2, x0, x1);
                     } else {
-                        x = __fdiv_rn(a, d.b);
+                        x0 = __fdiv_rn(av[4 * k + j], d.b); x1 = __fdiv_rn(av[4 * k + j + 1], d.b);
                     }
                     if (SR) {
-                        const float mag = fminf(__fadd_rn(fabsf(x), nz[4 * k + j]), 127.f);
-                        x = __uint_as_float(__float_as_uint(mag) ^ (__float_as_uint(x) & 0x80000000u));
+                        const float m0 = fminf(__fadd_rn(fabsf(x0), nz[4 * k + j]), 127.f), m1 = fminf(__fadd_rn(fabsf(x1), nz[4 * k + j + 1]), 127.f);
+                        x0 = __uint_as_float(__float_as_uint(m0) ^ (__float_as_uint(x0) & 0x80000000u));
+                        x1 = __uint_as_float(__float_as_uint(m1) ^ (__float_as_uint(x1) & 0x80000000u));
                     }
-                    b[j] = TRUNC ? (uint32_t)__float2int_rz(x) : __float_as_uint(__fadd_rn(x, 12582912.0f));
+                    b[j] = TRUNC ? (uint32_t)__float2int_rz(x0) : __float_as_uint(__fadd_rn(x0, 12582912.0f));
+                    b[j + 1] = TRUNC ? (uint32_t)__float2int_rz(x1) : __float_as_uint(__fadd_rn(x1, 12582912.0f));
                 }
                 words[k] = zero ? 0u : gather_bytes(b[0], b[1], b[2], b[3]);
             }
@@ -419,7 +426,7 @@ dequantize_kernel(const int8_t* __restrict__ q, const __half* __restrict__ s, in
             const uint32_t lo = __byte_perm(wx, 0x64646464u, 0x5140), hi = __byte_perm(wx, 0x64646464u, 0x5342);
             const float2 a = __half22float2(__hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&lo), bias), s2));
             const float2 b = __half22float2(__hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&hi), bias), s2));
-            *reinterpret_cast<float4*>(dst + (int64_t)(r0 + r) * N) = make_float4(a.x, a.y, b.x, b.y);
+            __stcs(reinterpret_cast<float4*>(dst + (int64_t)(r0 + r) * N), make_float4(a.x, a.y, b.x, b.y));   // written once, read by a later kernel
         }
     }
 }
@@ -643,19 +650,32 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
         });
 }
 
-// Correctly rounded fp32 values of the two transcendental functions of the GELU derivative at x >= 0, as the reference's
-// arithmetic defines them:  er = RN(erf(u)) with u = RN(x / sqrt2),  e = RN(exp(a)) with a = RN(-RN(x*x)/2)  (fp32 roundings RN):
-// evaluated in fp64 and rounded once.  (Two cheaper-looking forms measured no faster on B200 -- one shared fp64 exponential with
-// erf = 1 - exp(-u^2) erfcx(u), erfcx from the math library or from a degree-18 polynomial: 67.1 / 63.3 us against 62.6 us on
-// [8192 x 3072] -- the table build is bound by instruction issue, not by the fp64 pipe, which is 18 % busy.)
-__device__ __forceinline__ void gelu_bwd_erf_exp(float x, float& er, float& e) {
-    er = (float)erf((double)__fdiv_rn(x, SQRT2_F));
-    e = (float)exp((double)__fmul_rn(__fmul_rn(x, x), -0.5f));
+// The derivative table.  d(x) = Phi(x) + x*phi(x) is needed at x = q*s for the 256 payloads q of a block with scale s, i.e. at
+// |x| = a*s for a = 1..128 and each of the 32768 non-negative fp16 bit patterns of s: 4 M arguments in all.  The device table
+// holds, per (s, a), the pair ( d(+a*s), d(-a*s) ) evaluated with the reference's fp32 roundings
+//      er = RN(erf(u)), u = RN(x / sqrt2);   e = RN(exp(RN(-RN(x*x)/2)));   ex = RN(RN(x / sqrt(2 pi)) * e)
+//      d(+x) = RN(RN(0.5*(1 + er)) + ex),    d(-x) = RN(RN(0.5*(1 - er)) - ex)
+// where erf and exp are correctly rounded (fp64, rounded once).  32 MB, filled once per device by one kernel (a millisecond);
+// a block reads its row of 1 KB (lane l the pairs a = 4l+1..4l+4), which replaces 128 fp64 erf + exp evaluations per block --
+// the part that bound the kernel (instruction issue, not the fp64 pipe).  Rows in use cluster (scales of neighbouring blocks
+// share their exponent), so the reads are served by L2.
+constexpr uint32_t GELU_BWD_ROWS = 32768u;
+__device__ float2 g_gelu_bwd_table[GELU_BWD_ROWS * 128u];
+
+__global__ void gelu_bwd_table_kernel() {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= GELU_BWD_ROWS * 128u) return;
+    const float scx = __half2float(__ushort_as_half((unsigned short)(i >> 7)));
+    const float x = __fmul_rn((float)((i & 127u) + 1u), scx);                    // exact
+    const float er = (float)erf((double)__fdiv_rn(x, SQRT2_F));
+    const float e = (float)exp((double)__fmul_rn(__fmul_rn(x, x), -0.5f));
+    const float ex = __fmul_rn(__fdiv_rn(x, SQRT2PI_F), e);
+    g_gelu_bwd_table[i] = make_float2(__fadd_rn(__fmul_rn(0.5f, __fadd_rn(1.0f, er)), ex),
+                                      __fsub_rn(__fmul_rn(0.5f, __fsub_rn(1.0f, er)), ex));
 }
 
 // backward: x = q*s, g = qg*sg in fp32; d = (Phi(x) + x*phi(x)) * g; block quantise (+SR).
-// The table holds Phi(x) + x*phi(x) for the 256 payload values of the block.  erf and exp are odd / even in x, so one fp64
-// evaluation of each serves +q and -q: 128 evaluations per block, four per lane.
+// Per block the 256-entry table "payload -> d(q*s)" is copied from the block's row of the device table into shared memory.
 template <bool SR>
 __global__ void __launch_bounds__(THREADS, 3)
 gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, const int8_t* __restrict__ qg,
@@ -673,17 +693,15 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
             r.sb = load_scale16(sg, t, N);
         },
         [&](const Tile& t, Raw& r) {
-            const float scx = __half2float(r.sa);
+            // a negative or NaN scale (never produced by a quantiser) indexes by its magnitude bits
+            const float4* row = reinterpret_cast<const float4*>(g_gelu_bwd_table + ((uint32_t)(__half_as_ushort(r.sa) & 0x7FFFu) << 7)) + 2 * t.lane;
+            const float4 p01 = __ldg(row), p23 = __ldg(row + 1);       // pairs a = 4l+1, 4l+2 | 4l+3, 4l+4
             __syncwarp();   // the previous tile's lookups are done
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int a = 4 * t.lane + 1 + j;                        // |q| = 1 .. 128
-                const float x = __fmul_rn((float)a, scx);                // exact
-                float er, e;
-                gelu_bwd_erf_exp(x, er, e);
-                const float ex = __fmul_rn(__fdiv_rn(x, SQRT2PI_F), e);
-                if (a < 128) lut[a] = __fadd_rn(__fmul_rn(0.5f, __fadd_rn(1.0f, er)), ex);
-                lut[256 - a] = __fsub_rn(__fmul_rn(0.5f, __fsub_rn(1.0f, er)), ex);
+            {
+                const int a = 4 * t.lane + 1;
+                lut[a] = p01.x; lut[a + 1] = p01.z; lut[a + 2] = p23.x;
+                if (a + 3 < 128) lut[a + 3] = p23.z;                   // +128 is not a payload: that byte is -128's
+                lut[256 - a] = p01.y; lut[255 - a] = p01.w; lut[254 - a] = p23.y; lut[253 - a] = p23.w;
             }
             if (t.lane == 0) lut[0] = 0.5f;
             __syncwarp();
@@ -892,6 +910,7 @@ __device__ __forceinline__ void emit_block4(RowF&& rowf /* i -> the lane's float
     const Divisor d = make_divisor(scale32);
     const bool zero = (scale32 == 0.f);
     const bool fast = d.fast || zero;                      // identical in every lane: one divisor per block
+    const uint64_t inv2 = f2_pack(d.inv, d.inv), negb2 = f2_pack(-d.b, -d.b), magic2 = f2_pack(12582912.0f, 12582912.0f);
     auto rows = [&](auto fast_c) {
         constexpr bool FAST = decltype(fast_c)::value;
 #pragma unroll
@@ -929,19 +948,26 @@ __device__ __forceinline__ void emit_block4(RowF&& rowf /* i -> the lane's float
                 const float a[4] = {vi.x, vi.y, vi.z, vi.w};
                 uint32_t bts[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float x;
+                for (int k = 0; k < 4; k += 2) {
+                    float x0, x1;
                     if (FAST) {
-                        const float q0 = __fmul_rn(a[k], d.inv);
-                        x = __fmaf_rn(__fmaf_rn(-d.b, q0, a[k]), d.inv, q0);
+                        const uint64_t x2 = f2_div_fast(f2_pack(a[k], a[k + 1]), inv2, negb2);
+                        if (!SR && !TRUNC) {
+                            f2_unpack(f2_add(x2, magic2), x0, x1);
+                            bts[k] = __float_as_uint(x0); bts[k + 1] = __float_as_uint(x1);
+                            continue;
+                        }
+                        f2_unpack(x2, x0, x1);
                     } else {
-                        x = __fdiv_rn(a[k], d.b);
+                        x0 = __fdiv_rn(a[k], d.b); x1 = __fdiv_rn(a[k + 1], d.b);
                     }
                     if (SR) {
-                        const float mag = fminf(__fadd_rn(fabsf(x), nz[h][k]), 127.f);
-                        x = __uint_as_float(__float_as_uint(mag) ^ (__float_as_uint(x) & 0x80000000u));
+                        const float m0 = fminf(__fadd_rn(fabsf(x0), nz[h][k]), 127.f), m1 = fminf(__fadd_rn(fabsf(x1), nz[h][k + 1]), 127.f);
+                        x0 = __uint_as_float(__float_as_uint(m0) ^ (__float_as_uint(x0) & 0x80000000u));
+                        x1 = __uint_as_float(__float_as_uint(m1) ^ (__float_as_uint(x1) & 0x80000000u));
                     }
-                    bts[k] = TRUNC ? (uint32_t)__float2int_rz(x) : __float_as_uint(__fadd_rn(x, 12582912.0f));
+                    bts[k] = TRUNC ? (uint32_t)__float2int_rz(x0) : __float_as_uint(__fadd_rn(x0, 12582912.0f));
+                    bts[k + 1] = TRUNC ? (uint32_t)__float2int_rz(x1) : __float_as_uint(__fadd_rn(x1, 12582912.0f));
                 }
                 const uint32_t word = zero ? 0u : gather_bytes(bts[0], bts[1], bts[2], bts[3]);
                 *reinterpret_cast<uint32_t*>(qy + base + (int64_t)(4 * i) * N) = word;
@@ -1210,30 +1236,37 @@ static void launch_quantize(const void* x, int64_t M, int64_t N, int8_t* q, __ha
     }
 }
 
-// The GELU-forward table of the current device: filled by one kernel launch on the first call's stream; until that launch is
+// The GELU tables (forward: 256 KB, backward: 32 MB) of the current device: each filled by one kernel launch on the first call's stream; until that launch is
 // known to have finished, calls on any stream wait for its event.
 struct FwdTableState {
     cudaEvent_t ready = nullptr;
     bool launched = false, complete = false;
 };
-static FwdTableState g_fwd_table[64];
+static FwdTableState g_fwd_table[64], g_bwd_table[64];
 static std::mutex g_fwd_table_mutex;
 
-static int ensure_gelu_fwd_table(cudaStream_t st) {
+static int ensure_gelu_table(cudaStream_t st, bool backward) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JF_ERR_UNSUPPORTED;
     std::lock_guard<std::mutex> lock(g_fwd_table_mutex);
-    FwdTableState& ts = g_fwd_table[dev];
+    FwdTableState& ts = (backward ? g_bwd_table : g_fwd_table)[dev];
     if (ts.complete) return JF_OK;
     if (!ts.launched) {
+        cudaStreamCaptureStatus cap0 = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap0) != cudaSuccess) return JF_ERR_LAUNCH;
+        if (cap0 != cudaStreamCaptureStatusNone) return JF_ERR_UNSUPPORTED;     // the fill must not become part of a graph
         if (cudaEventCreateWithFlags(&ts.ready, cudaEventDisableTiming) != cudaSuccess) return JF_ERR_LAUNCH;
-        gelu_fwd_table_kernel<<<256, 256, 0, st>>>();
+        if (backward) gelu_bwd_table_kernel<<<GELU_BWD_ROWS * 128u / 256u, 256, 0, st>>>();
+        else gelu_fwd_table_kernel<<<256, 256, 0, st>>>();
         if (int e = check_launch()) return e;
         if (cudaEventRecord(ts.ready, st) != cudaSuccess) return JF_ERR_LAUNCH;
         ts.launched = true;
         return JF_OK;   // later work on `st` is ordered after the fill
     }
-    if (cudaEventQuery(ts.ready) == cudaSuccess) {
+    // a stream that is being captured must not be queried: order the captured work after the fill instead
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) return JF_ERR_LAUNCH;
+    if (cap == cudaStreamCaptureStatusNone && cudaEventQuery(ts.ready) == cudaSuccess) {
         ts.complete = true;
         return JF_OK;
     }
@@ -1347,7 +1380,7 @@ int jf_int8_gelu_forward(const int8_t* qx, const void* sx, int64_t M, int64_t N,
     if (int e = check_mn(M, N)) return e;
     JF_REQUIRE_ALIGNED(qx); JF_REQUIRE_ALIGNED(qy);
     cudaStream_t st = (cudaStream_t)stream;
-    if (int e = ensure_gelu_fwd_table(st)) return e;
+    if (int e = ensure_gelu_table(st, false)) return e;
     gelu_fwd_kernel<<<grid_for<32>(M, N, persistent_ctas(3)), THREADS, 0, st>>>(qx, (const __half*)sx, M, N, qy, (__half*)sy);
     return check_launch();
 }
@@ -1361,6 +1394,7 @@ int jf_int8_gelu_backward(const int8_t* qx, const void* sx, const int8_t* qg, co
     SrCfg sr = make_sr(noise, seed, offset);
     cudaStream_t st = (cudaStream_t)stream;
     const __half* sxh = (const __half*)sx; const __half* sgh = (const __half*)sg; __half* sdh = (__half*)sd;
+    if (int e = ensure_gelu_table(st, true)) return e;
     const unsigned grid = grid_for<32>(M, N, persistent_ctas(3));
     if (stochastic) gelu_bwd_kernel<true><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr);
     else gelu_bwd_kernel<false><<<grid, THREADS, 0, st>>>(qx, sxh, qg, sgh, M, N, qd, sdh, sr);

@@ -8,7 +8,9 @@ nothing is copied, the only output is `oracle/_ref/BlockQuantizeCUDA.so` (git-ig
 kernels recompiled for Blackwell's legacy tensor path.  They serve two purposes, both on a GPU box only:
   * a second pin of the GEMM oracle: the reference's own kernels against the CPU restatement at the reference's own test
     shapes (tolerance-level, the reference builds with -use_fast_math), tests/test_gpu_reference_ext.py;
-  * the GPU-side baseline timing of `bench.py --workload gemm_sweep`.
+  * the GPU-side baseline timing of `bench.py --impl reference --workload gemm_sweep`.
+`load_nonlinear()` imports the reference's Triton operators (Jetfire/Nonlinear/*.py, nothing to build) for the same two uses:
+tests/test_gpu_reference_triton.py and `bench.py --impl reference --workload nonlinear`.
 The checkout is found through --reference, $JETFIRE_REFERENCE, or /root/reference; without one this script does nothing.
 """
 import os
@@ -93,6 +95,54 @@ def load():
     spec = importlib.util.spec_from_file_location("BlockQuantizeCUDA", OUT)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
+    return mod
+
+
+def nonlinear_root():
+    """Directory holding the reference's Jetfire/Nonlinear/*.py: a checkout ($JETFIRE_REFERENCE, /root/reference) or the copies
+    that tests/stage_reference.py staged into baseline/_ref/ (git-ignored) so that they exist on a GPU box."""
+    staged = os.path.join(os.path.dirname(HERE), "baseline", "_ref")
+    for cand in (os.environ.get("JETFIRE_REFERENCE"), "/root/reference", staged):
+        if cand and os.path.exists(os.path.join(cand, "Jetfire", "Nonlinear", "layernorm.py")):
+            return cand
+    return None
+
+
+def load_nonlinear(first_config_only=False):
+    """The reference's `Jetfire.Nonlinear` package (its Triton kernels, unmodified), imported under the private module name
+    `_reference_jetfire_nonlinear` so that it never collides with the `Jetfire` name the drop-in shim registers; None when no
+    reference files are reachable.  `first_config_only` cuts every kernel's autotuner to its first configuration (tile shape and
+    stage count do not change results) to keep compilation short in parity tests; timing runs keep the full search."""
+    import importlib
+    import importlib.util
+    root = nonlinear_root()
+    if root is None:
+        return None
+    name = "_reference_jetfire_nonlinear"
+    mod = sys.modules.get(name)
+    if mod is None:
+        pkg = os.path.join(root, "Jetfire", "Nonlinear")
+        spec = importlib.util.spec_from_file_location(name, os.path.join(pkg, "__init__.py"), submodule_search_locations=[pkg])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        try:
+            spec.loader.exec_module(mod)
+        except Exception:
+            del sys.modules[name]
+            raise
+        # dequantize.py is not re-exported by the package's __init__ (Jetfire/Nonlinear/__init__.py:1-8)
+        mod.int8_dequantize = importlib.import_module(name + ".dequantize").int8_dequantize
+    if first_config_only:
+        from triton.runtime.autotuner import Autotuner
+        for sub in ("add", "add_mean_var", "dequantize", "gelu_bwd", "gelu_fwd", "layernorm", "quantize", "quantize_transpose",
+                    "transpose"):
+            m = importlib.import_module(name + "." + sub)
+            for attr in dir(m):
+                k = getattr(m, attr)
+                while k is not None and not isinstance(k, Autotuner):
+                    k = getattr(k, "fn", None)
+                if k is not None:
+                    k.configs = k.configs[:1]
     return mod
 
 

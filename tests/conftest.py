@@ -55,3 +55,9 @@ def oracle():
     from oracle import jetfire_oracle as O
     O.build_c_oracle()
     return O
+
+
+@pytest.fixture(scope="session")
+def NL():
+    from jetfire_int8training_b200 import Nonlinear
+    return Nonlinear

@@ -4,9 +4,10 @@ extension into oracle/_ref/ (oracle/build_ref.py).
 
     python tests/stage_reference.py [--reference /path/to/Jetfire-INT8Training]
 
-Staged: INT8_GPT2/qmodel.py (the caller of the hot path) and Jetfire/Linear/{__init__,linear_fwd,linear_bwd}.py (the glue on
-top of the `BlockQuantizeCUDA` extension).  tests/test_gpu_dropin.py skips when neither $JETFIRE_REFERENCE nor baseline/_ref
-holds them.  Nothing staged here is imported by the package, by bench.py's timed region or by any CPU test.
+Staged: INT8_GPT2/qmodel.py (the caller of the hot path), Jetfire/Linear/{__init__,linear_fwd,linear_bwd}.py (the glue on
+top of the `BlockQuantizeCUDA` extension) and the Triton operators Jetfire/Nonlinear/*.py.  tests/test_gpu_dropin.py and
+tests/test_gpu_reference_triton.py skip when neither $JETFIRE_REFERENCE nor baseline/_ref holds them.  Nothing staged here is
+imported by the package, by the timed region of bench.py's own arm or by any CPU test.
 """
 import os
 import shutil
@@ -15,6 +16,8 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 STAGE = os.path.join(ROOT, "baseline", "_ref")
 FILES = ["INT8_GPT2/qmodel.py", "Jetfire/Linear/__init__.py", "Jetfire/Linear/linear_fwd.py", "Jetfire/Linear/linear_bwd.py"]
+FILES += [f"Jetfire/Nonlinear/{m}.py" for m in ("__init__", "add", "add_mean_var", "common", "dequantize", "gelu_bwd", "gelu_fwd",
+                                                "layernorm", "quantize", "quantize_transpose", "transpose", "utils")]
 
 
 def reference_files_root():

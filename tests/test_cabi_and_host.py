@@ -99,3 +99,11 @@ def test_sr_key_stream():
     from jetfire_int8training_b200 import rng
     rng.manual_seed(123, 10)
     assert rng.next_key() == (123, 10) and rng.next_key() == (123, 11)
+
+
+def test_sr_noise_mode_switch():
+    from jetfire_int8training_b200 import Nonlinear as NL
+    prev = NL.set_sr_noise("torch")
+    assert prev == "philox" and NL.set_sr_noise(prev) == "torch"
+    with pytest.raises(ValueError):
+        NL.set_sr_noise("curand")

@@ -18,12 +18,6 @@ from gpu_util import DEV, assert_bits_equal, n, outlier_randn, t
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def NL():
-    from jetfire_int8training_b200 import Nonlinear
-    return Nonlinear
-
-
 # ------------------------------------------------------------------------------------------------ golden vectors
 @pytest.mark.parametrize("tag,dt", [("f32", torch.float32), ("f16", torch.float16), ("bf16", torch.bfloat16)])
 def test_quantize_golden(NL, tag, dt):
