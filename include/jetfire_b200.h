@@ -71,7 +71,7 @@ int jf_int8_dequantize(const int8_t* q, const void* s, int64_t M, int64_t N, flo
 int jf_int8_transpose(const int8_t* x, int64_t M, int64_t N, int8_t* y, void* stream);
 
 /* int8_gelu_forward(x, s_x, QB)               Jetfire/Nonlinear/gelu_fwd.py:128-162 (kernel :34-126)
- * Both GELU entry points use a per-device table in device memory (forward 256 KB, backward 32 MB, static storage of the library)
+ * Both GELU entry points use a per-device table in device memory (32 MB each, static storage of the library)
  * that the first call on a device fills with one extra kernel on that call's stream; later calls on other streams wait for the
  * fill through an event.  That first call must not be made on a stream that is being captured (JF_ERR_UNSUPPORTED). */
 int jf_int8_gelu_forward(const int8_t* qx, const void* sx, int64_t M, int64_t N, int8_t* qy, void* sy, void* stream);

@@ -487,18 +487,22 @@ transpose_kernel(const int8_t* __restrict__ x, int64_t M, int64_t N, int8_t* __r
 constexpr float SQRT2_F = 1.41421353816986083984375f;      // sqrt(2) rounded to fp32 (the reference divides by this value)
 constexpr float SQRT2PI_F = 2.50662827491760253906250f;    // fp32 sqrt of fp32(2*pi)
 
-// Forward: the input of the function is the fp16 product x = fp16(q * s), so y(x) = x * Phi(x) has only 65536 possible arguments.
-// They are tabulated once per device (256 KB, stays in L2): entry = bit pattern of x.
-__device__ float g_gelu_fwd_table[65536];
+// Forward table.  y(x) = x * Phi(x) is needed at x = fp16(q * s) for the 256 payloads q of a block with scale s, i.e. at
+// +-x for x = fp16(a * s), a = 1..128, and each of the 32768 non-negative fp16 bit patterns of s.  The device table holds, per
+// (s, a), the pair ( y(+x), y(-x) ) with the reference's fp32 roundings and a correctly rounded erf (fp64, rounded once):
+//      er = RN(erf(RN(x / sqrt2)));   y(+x) = RN(RN(RN(1 + er) / 2) * x),   y(-x) = RN(RN(RN(1 - er) / 2) * -x).
+// 32 MB, filled once per device by one kernel; a block reads its row of 1 KB (lane l the pairs a = 4l+1 .. 4l+4).
+constexpr uint32_t GELU_ROWS = 32768u;
+__device__ float2 g_gelu_fwd_table[GELU_ROWS * 128u];
 
 __global__ void gelu_fwd_table_kernel() {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= 65536u) return;
-    const float x = __half2float(__ushort_as_half((unsigned short)i));
-    const float u = __fdiv_rn(x, SQRT2_F);
-    const float er = (float)erf((double)u);
-    const float cdf = __fmul_rn(__fadd_rn(1.0f, er), 0.5f);   // (1 + erf) / 2: the halving is exact
-    g_gelu_fwd_table[i] = __fmul_rn(cdf, x);
+    if (i >= GELU_ROWS * 128u) return;
+    const __half x16 = __hmul_rn(__int2half_rn((int)(i & 127u) + 1), __ushort_as_half((unsigned short)(i >> 7)));   // the reference's fp16 product
+    const float x = __half2float(x16);
+    const float er = (float)erf((double)__fdiv_rn(x, SQRT2_F));          // erf is odd: RN(erf(-u)) = -RN(erf(u))
+    g_gelu_fwd_table[i] = make_float2(__fmul_rn(__fmul_rn(__fadd_rn(1.0f, er), 0.5f), x),
+                                      __fmul_rn(__fmul_rn(__fsub_rn(1.0f, er), 0.5f), -x));
 }
 
 // address of entry `byte k of w` of a 256-byte table that starts at the 256-byte-aligned shared address `base`
@@ -531,26 +535,19 @@ __device__ __forceinline__ void lookup16(const float* lut_b, const int4& r, floa
 }
 
 // forward: x = fp16(q*s); y = x * Phi(x); block quantise with amax + 5e-5.
-// Per 32x32 block (= one warp tile) the kernel builds the table "input payload -> OUTPUT payload" (256 bytes) and translates
-// every element through it.  Exactness without evaluating erf exactly 256 times per block:
-//   (1) block absmax: y is non-decreasing for x > 0 and |y| < 0.17 for x < 0, so when y(largest positive payload) >= 0.17
-//       that value IS the absmax -- one SIMD byte max per four elements and ONE lookup of the exact device table;
-//   (2) table entries: lane l evaluates the magnitudes |q| = 4l+1 .. 4l+4 with erff (<= 2 ulp) and derives the entries of +q
-//       and -q.  The approximate quotient differs from the exact one by less than `margin` (bound below); when it lies further
-//       than that from a rounding boundary its rounding IS the exact payload, otherwise (a few entries in 10^4) the entry is
-//       recomputed from the exact device table with the exact division;
-//   (3) a block of small inputs (absmax below 0.17, rare) takes the exact table for everything.
-// Error bound of (2): |erff - erf| <= 2 ulp <= 1.2e-7, the argument x*0.70710678f differs from the reference's x/sqrt(2) by
-// <= 1.5 ulp (<= 0.9e-7 in erf), the exact erf is itself rounded (3e-8); (1 +- erf)/2 and the product with x round once more
-// in both chains: |y~ - y| <= 3e-7 |x|.  The test uses twice that, plus 4e-5 for the roundings of the quotient itself.
-__device__ __forceinline__ float gelu_table(const __half x16) { return __ldg(&g_gelu_fwd_table[__half_as_ushort(x16)]); }
-
+// Per 32x32 block (= one warp tile) the kernel builds the table "input payload -> OUTPUT payload" (256 bytes) from the block's
+// row of the device table and translates every element through it:
+//   (1) block absmax: y is non-decreasing for x > 0 and |y| < 0.17 for x < 0, so when y(largest positive payload) >= 0.17 that
+//       value IS the absmax -- one SIMD byte max per four elements, no per-element arithmetic;
+//   (2) table entries: lane l divides its eight exact y values (a = 4l+1 .. 4l+4, both signs) by the block scale -- the exact
+//       quotient is the Markstein sequence with the correctly rounded reciprocal, valid because scale32 >= 0.17/127;
+//   (3) a block of small inputs (absmax below 0.17, rare) finds its absmax over the elements and divides with div.rn.
 __global__ void __launch_bounds__(THREADS, 3)
 gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, int64_t M, int64_t N, int8_t* __restrict__ qy,
                 __half* __restrict__ sy) {
     constexpr int TW = 32, NP = Geo<TW>::NP;
     using Raw = RawQ<NP>;
-    __shared__ __align__(16) float ytab_all[WARPS][256];          // slow path only
+    __shared__ __align__(16) float ytab_all[WARPS][256];          // path (3) only
     __shared__ __align__(256) uint8_t btab_all[WARPS][256];
     const int warp = threadIdx.x >> 5;
     float* ytab = ytab_all[warp];
@@ -564,6 +561,10 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
         },
         [&](const Tile& t, Raw& r) {
             const int lane = t.lane;
+            // the block's table row (a negative or NaN scale, never produced by a quantiser, indexes by its magnitude bits)
+            const float4* row = reinterpret_cast<const float4*>(g_gelu_fwd_table + ((uint32_t)(__half_as_ushort(r.sc) & 0x7FFFu) << 7)) + 2 * lane;
+            const float4 p01 = __ldg(row), p23 = __ldg(row + 1);
+            const float yp[4] = {p01.x, p01.z, p23.x, p23.z}, yn[4] = {p01.y, p01.w, p23.y, p23.w};   // y(+a s), y(-a s), a = 4l+1 ..
             // largest payload of the block
             uint32_t m4 = 0x80808080u;   // four int8 -128
 #pragma unroll
@@ -574,16 +575,18 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
             m4 = __vmaxs4(m4, m4 >> 16);
             m4 = __vmaxs4(m4, m4 >> 8);
             const int qmax = __reduce_max_sync(0xffffffffu, (int)(int8_t)(m4 & 0xFFu));
-            float amax = qmax > 0 ? gelu_table(__hmul_rn(__int2half_rn(qmax), r.sc)) : 0.f;
+            const int im = (qmax > 0 ? qmax : 1) - 1, cm = im & 3;
+            const float ym = __shfl_sync(0xffffffffu, cm == 0 ? yp[0] : cm == 1 ? yp[1] : cm == 2 ? yp[2] : yp[3], im >> 2);
+            float amax = qmax > 0 ? ym : 0.f;
             const bool fast_tile = amax >= 0.17f;     // warp-uniform
             __syncwarp();                             // the previous tile's translation is done
             if (!fast_tile) {
-                // (3) every table entry from the exact device table, absmax over the elements
-                float y[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) y[j] = gelu_table(__hmul_rn(__int2half_rn((int)(int8_t)(uint8_t)(8 * lane + j)), r.sc));
-                *reinterpret_cast<float4*>(ytab + 8 * lane) = make_float4(y[0], y[1], y[2], y[3]);
-                *reinterpret_cast<float4*>(ytab + 8 * lane + 4) = make_float4(y[4], y[5], y[6], y[7]);
+                // (3) absmax over the elements, through the fp32 table of the block
+                const int a = 4 * lane + 1;
+                ytab[a] = yp[0]; ytab[a + 1] = yp[1]; ytab[a + 2] = yp[2];
+                if (a + 3 < 128) ytab[a + 3] = yp[3];                  // +128 is not a payload: that byte is -128's
+                ytab[256 - a] = yn[0]; ytab[255 - a] = yn[1]; ytab[254 - a] = yn[2]; ytab[253 - a] = yn[3];
+                if (lane == 0) ytab[0] = 0.f;
                 __syncwarp();
                 float m = 0.f;
 #pragma unroll
@@ -594,50 +597,34 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
                     for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(f[j]));
                 }
                 amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
-                const float scale32 = __fdiv_rn(__fadd_rn(amax, 5e-5f), 127.0f);
-                uint32_t b[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(__fadd_rn(__fdiv_rn(y[j], scale32), 12582912.0f));
-                *reinterpret_cast<uint2*>(btab_g + 8 * lane) = make_uint2(gather_bytes(b[0], b[1], b[2], b[3]), gather_bytes(b[4], b[5], b[6], b[7]));
             }
             const float scale32 = __fdiv_rn(__fadd_rn(amax, 5e-5f), 127.0f);
+            uint32_t bp[4], bn[4];
             if (fast_tile) {
-                // (2) scale32 >= 0.17/127: the exact quotient is the Markstein sequence with the correctly rounded reciprocal
                 const float inv = __frcp_rn(scale32);
-                uint32_t bp[4], bn[4];
+                const uint64_t inv2 = f2_pack(inv, inv), negb2 = f2_pack(-scale32, -scale32), magic2 = f2_pack(12582912.0f, 12582912.0f);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int a = 4 * lane + 1 + j;                                   // |q| = 1 .. 128
-                    const __half x16 = __hmul_rn(__int2half_rn(a), r.sc);             // the reference's fp16 product (odd in q)
-                    const float x = __half2float(x16);
-                    const float er = erff(__fmul_rn(x, 0.70710678118654752f));
-                    const float hx = __fmul_rn(0.5f, x);
-                    const float yp = __fmul_rn(__fadd_rn(1.0f, er), hx), yn = -__fmul_rn(__fsub_rn(1.0f, er), hx);
-                    const float margin = __fmaf_rn(__fmul_rn(6e-7f, x), inv, 4e-5f);
-                    float vp = __fmul_rn(yp, inv), vn = __fmul_rn(yn, inv);
-                    float rp = __fadd_rn(vp, 12582912.0f), rn = __fadd_rn(vn, 12582912.0f);
-                    // distance of v to the integer it rounds to; beyond 0.5 - margin the exact value may round the other way.
-                    // (negated comparison: a NaN from an overflowing input takes the exact path as well)
-                    if (!(fabsf(__fsub_rn(vp, __fsub_rn(rp, 12582912.0f))) < __fsub_rn(0.5f, margin))) {
-                        const float y = gelu_table(x16), q0 = __fmul_rn(y, inv);
-                        rp = __fadd_rn(__fmaf_rn(__fmaf_rn(-scale32, q0, y), inv, q0), 12582912.0f);
-                    }
-                    if (!(fabsf(__fsub_rn(vn, __fsub_rn(rn, 12582912.0f))) < __fsub_rn(0.5f, margin))) {
-                        const float y = gelu_table(__hneg(x16)), q0 = __fmul_rn(y, inv);
-                        rn = __fadd_rn(__fmaf_rn(__fmaf_rn(-scale32, q0, y), inv, q0), 12582912.0f);
-                    }
+                    float rp, rn;
+                    f2_unpack(f2_add(f2_div_fast(f2_pack(yp[j], yn[j]), inv2, negb2), magic2), rp, rn);
                     bp[j] = __float_as_uint(rp); bn[j] = __float_as_uint(rn);
                 }
-                // entries 4l+1 .. 4l+4 (the last lane's +128 does not exist: that byte is -128's) and 252-4l .. 255-4l
-                if (lane < 31) {
-                    btab_g[4 * lane + 1] = (uint8_t)bp[0]; btab_g[4 * lane + 2] = (uint8_t)bp[1];
-                    btab_g[4 * lane + 3] = (uint8_t)bp[2]; btab_g[4 * lane + 4] = (uint8_t)bp[3];
-                } else {
-                    btab_g[125] = (uint8_t)bp[0]; btab_g[126] = (uint8_t)bp[1]; btab_g[127] = (uint8_t)bp[2];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    bp[j] = __float_as_uint(__fadd_rn(__fdiv_rn(yp[j], scale32), 12582912.0f));
+                    bn[j] = __float_as_uint(__fadd_rn(__fdiv_rn(yn[j], scale32), 12582912.0f));
                 }
-                *reinterpret_cast<uint32_t*>(btab_g + 252 - 4 * lane) = gather_bytes(bn[3], bn[2], bn[1], bn[0]);
-                if (lane == 0) btab_g[0] = 0;          // y(0) = 0
             }
+            // entries 4l+1 .. 4l+4 (the last lane's +128 does not exist: that byte is -128's) and 252-4l .. 255-4l
+            if (lane < 31) {
+                btab_g[4 * lane + 1] = (uint8_t)bp[0]; btab_g[4 * lane + 2] = (uint8_t)bp[1];
+                btab_g[4 * lane + 3] = (uint8_t)bp[2]; btab_g[4 * lane + 4] = (uint8_t)bp[3];
+            } else {
+                btab_g[125] = (uint8_t)bp[0]; btab_g[126] = (uint8_t)bp[1]; btab_g[127] = (uint8_t)bp[2];
+            }
+            *reinterpret_cast<uint32_t*>(btab_g + 252 - 4 * lane) = gather_bytes(bn[3], bn[2], bn[1], bn[0]);
+            if (lane == 0) btab_g[0] = 0;          // y(0) = 0
             __syncwarp();
             // translate and store
 #pragma unroll
@@ -659,12 +646,11 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
 // a block reads its row of 1 KB (lane l the pairs a = 4l+1..4l+4), which replaces 128 fp64 erf + exp evaluations per block --
 // the part that bound the kernel (instruction issue, not the fp64 pipe).  Rows in use cluster (scales of neighbouring blocks
 // share their exponent), so the reads are served by L2.
-constexpr uint32_t GELU_BWD_ROWS = 32768u;
-__device__ float2 g_gelu_bwd_table[GELU_BWD_ROWS * 128u];
+__device__ float2 g_gelu_bwd_table[GELU_ROWS * 128u];
 
 __global__ void gelu_bwd_table_kernel() {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= GELU_BWD_ROWS * 128u) return;
+    if (i >= GELU_ROWS * 128u) return;
     const float scx = __half2float(__ushort_as_half((unsigned short)(i >> 7)));
     const float x = __fmul_rn((float)((i & 127u) + 1u), scx);                    // exact
     const float er = (float)erf((double)__fdiv_rn(x, SQRT2_F));
@@ -1236,7 +1222,7 @@ static void launch_quantize(const void* x, int64_t M, int64_t N, int8_t* q, __ha
     }
 }
 
-// The GELU tables (forward: 256 KB, backward: 32 MB) of the current device: each filled by one kernel launch on the first call's stream; until that launch is
+// The GELU tables (32 MB each) of the current device: each filled by one kernel launch on the first call's stream; until that launch is
 // known to have finished, calls on any stream wait for its event.
 struct FwdTableState {
     cudaEvent_t ready = nullptr;
@@ -1256,8 +1242,8 @@ static int ensure_gelu_table(cudaStream_t st, bool backward) {
         if (cudaStreamIsCapturing(st, &cap0) != cudaSuccess) return JF_ERR_LAUNCH;
         if (cap0 != cudaStreamCaptureStatusNone) return JF_ERR_UNSUPPORTED;     // the fill must not become part of a graph
         if (cudaEventCreateWithFlags(&ts.ready, cudaEventDisableTiming) != cudaSuccess) return JF_ERR_LAUNCH;
-        if (backward) gelu_bwd_table_kernel<<<GELU_BWD_ROWS * 128u / 256u, 256, 0, st>>>();
-        else gelu_fwd_table_kernel<<<256, 256, 0, st>>>();
+        if (backward) gelu_bwd_table_kernel<<<GELU_ROWS * 128u / 256u, 256, 0, st>>>();
+        else gelu_fwd_table_kernel<<<GELU_ROWS * 128u / 256u, 256, 0, st>>>();
         if (int e = check_launch()) return e;
         if (cudaEventRecord(ts.ready, st) != cudaSuccess) return JF_ERR_LAUNCH;
         ts.launched = true;
