@@ -534,6 +534,18 @@ __device__ __forceinline__ void lookup16(const float* lut_b, const int4& r, floa
         }
 }
 
+// A lane's share of a table row: the pairs a = 4l+1, 4l+2 | 4l+3, 4l+4 of the row selected by the block scale (a negative or NaN
+// scale, never produced by a quantiser, indexes by its magnitude bits).
+struct TableRow {
+    float4 p01, p23;
+};
+__device__ __forceinline__ TableRow load_table_row(const float2* table, __half sc, int lane) {
+    const float4* row = reinterpret_cast<const float4*>(table + ((uint32_t)(__half_as_ushort(sc) & 0x7FFFu) << 7)) + 2 * lane;
+    TableRow r;
+    r.p01 = __ldg(row); r.p23 = __ldg(row + 1);
+    return r;
+}
+
 // forward: x = fp16(q*s); y = x * Phi(x); block quantise with amax + 5e-5.
 // Per 32x32 block (= one warp tile) the kernel builds the table "input payload -> OUTPUT payload" (256 bytes) from the block's
 // row of the device table and translates every element through it:
@@ -561,9 +573,8 @@ gelu_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, in
         },
         [&](const Tile& t, Raw& r) {
             const int lane = t.lane;
-            // the block's table row (a negative or NaN scale, never produced by a quantiser, indexes by its magnitude bits)
-            const float4* row = reinterpret_cast<const float4*>(g_gelu_fwd_table + ((uint32_t)(__half_as_ushort(r.sc) & 0x7FFFu) << 7)) + 2 * lane;
-            const float4 p01 = __ldg(row), p23 = __ldg(row + 1);
+            const TableRow tr = load_table_row(g_gelu_fwd_table, r.sc, lane);
+            const float4 p01 = tr.p01, p23 = tr.p23;
             const float yp[4] = {p01.x, p01.z, p23.x, p23.z}, yn[4] = {p01.y, p01.w, p23.y, p23.w};   // y(+a s), y(-a s), a = 4l+1 ..
             // largest payload of the block
             uint32_t m4 = 0x80808080u;   // four int8 -128
@@ -679,9 +690,8 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
             r.sb = load_scale16(sg, t, N);
         },
         [&](const Tile& t, Raw& r) {
-            // a negative or NaN scale (never produced by a quantiser) indexes by its magnitude bits
-            const float4* row = reinterpret_cast<const float4*>(g_gelu_bwd_table + ((uint32_t)(__half_as_ushort(r.sa) & 0x7FFFu) << 7)) + 2 * t.lane;
-            const float4 p01 = __ldg(row), p23 = __ldg(row + 1);       // pairs a = 4l+1, 4l+2 | 4l+3, 4l+4
+            const TableRow tr = load_table_row(g_gelu_bwd_table, r.sa, t.lane);
+            const float4 p01 = tr.p01, p23 = tr.p23;       // pairs a = 4l+1, 4l+2 | 4l+3, 4l+4
             __syncwarp();   // the previous tile's lookups are done
             {
                 const int a = 4 * t.lane + 1;
@@ -692,6 +702,7 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
             if (t.lane == 0) lut[0] = 0.5f;
             __syncwarp();
             const float scg = __half2float(r.sb);
+            const uint64_t scg2 = f2_pack(scg, scg);
             float v[NP][16];
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
@@ -699,7 +710,8 @@ gelu_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, co
                 lookup16(lut, r.a[i], fd);
                 unpack16(r.b[i], fg);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(fd[j], __fmul_rn(fg[j], scg));
+                for (int j = 0; j < 16; j += 2)
+                    f2_unpack(f2_mul(f2_pack(fd[j], fd[j + 1]), f2_mul(f2_pack(fg[j], fg[j + 1]), scg2)), v[i][j], v[i][j + 1]);
             }
             const float scale32 = __fdiv_rn(block_max<TW>(absmax_tile<NP>(v)), 127.0f);
             emit_quantized<TW, false, SR, false>([&](int i, float (&a)[16]) {
@@ -734,15 +746,20 @@ ln_fwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
 #pragma unroll
                 for (int j = 0; j < 16; ++j) gm[j] = 0.f;
             }
+            uint64_t gm2[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gm2[j] = f2_pack(gm[2 * j], gm[2 * j + 1]);
             float v[NP][16];
 #pragma unroll
             for (int i = 0; i < NP; ++i) {
                 const int64_t row = row_of<TW>(t, i);
                 const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+                const uint64_t nmu2 = f2_pack(-mu, -mu), rs2 = f2_pack(rs, rs);
                 float f[16];
                 dequant16_h(r.d[i], s2, f);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(__fmul_rn(__fsub_rn(f[j], mu), rs), gm[j]);
+                for (int j = 0; j < 8; ++j)        // ((f - mu) * rs) * gamma, two columns per instruction
+                    f2_unpack(f2_mul(f2_mul(f2_add(f2_pack(f[2 * j], f[2 * j + 1]), nmu2), rs2), gm2[j]), v[i][2 * j], v[i][2 * j + 1]);
             }
             const float scale32 = __fdiv_rn(block_max<TW>(absmax_tile<NP>(v)), 127.0f);
             SrCfg sr{};
@@ -834,10 +851,15 @@ ln_bwd_kernel(const int8_t* __restrict__ qx, const __half* __restrict__ sx, cons
             }
         }
         const float c1 = __fdiv_rn(tot.x, n_f), c2 = __fdiv_rn(tot.y, n_f);
+        const uint64_t nc1 = f2_pack(-c1, -c1), nc2 = f2_pack(-c2, -c2), rs_2 = f2_pack(rs, rs);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float tt = __fadd_rn(__fmul_rn(xh[j], c1), c2);
-            v[i][j] = __half2float(__float2half_rn(__fmul_rn(__fsub_rn(wdy[j], tt), rs)));
+        for (int j = 0; j < 16; j += 2) {
+            // (wdy - (xhat * c1 + c2)) * rstd, each operation rounded:  -(a*b + c) == (a * -b) + -c  exactly
+            const uint64_t ntt = f2_add(f2_mul(f2_pack(xh[j], xh[j + 1]), nc1), nc2);
+            float d0, d1;
+            f2_unpack(f2_mul(f2_add(f2_pack(wdy[j], wdy[j + 1]), ntt), rs_2), d0, d1);
+            const float2 dd = __half22float2(__floats2half2_rn(d0, d1));
+            v[i][j] = dd.x; v[i][j + 1] = dd.y;
         }
     }
     // partial dgamma: reduce the row groups, lanes with rg == 0 write 16 columns
