@@ -586,12 +586,13 @@ def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local
     mb = micro_batch or mb
     torch.manual_seed(1337)
     rng.manual_seed(1337 + rank)
+    from jetfire_int8training_b200.optim import ClipAdamW
     model = QGPT(cfg).to(dev)
-    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
     decay = [p for p in model.parameters() if p.dim() >= 2]
     nodecay = [p for p in model.parameters() if p.dim() < 2]
-    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": nodecay, "weight_decay": 0.0}], lr=6e-4,
-                            betas=(0.9, 0.95), fused=True)
+    # gradient clipping (max norm 1.0) + AdamW in one call; it re-points the parameters into one flat buffer, so before DDP
+    opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=6e-4, betas=(0.9, 0.95), max_norm=1.0)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
     g = torch.Generator(device=dev).manual_seed(rank)
     T = cfg.block_size
 
@@ -602,7 +603,6 @@ def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local
     def step(x, y):
         loss = net(x, y)
         loss.backward()
-        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
         opt.zero_grad(set_to_none=True)
         return loss

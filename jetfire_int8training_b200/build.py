@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libjetfire_b200.so")
-SOURCES = ["nonlinear.cu", "gemm.cu", "noalloc.cu", "lm_loss.cu"]
+SOURCES = ["nonlinear.cu", "gemm.cu", "noalloc.cu", "lm_loss.cu", "optim.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 

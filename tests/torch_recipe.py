@@ -63,6 +63,11 @@ def int8_quantize(x, B, stochastic=False, noise=None):
     return _unflat(q, bs), _unflat(s, bs)
 
 
+def int8_quantize_many(tensors, B):
+    """The weight quantisations of one step, one after the other (the package does them eight per launch)."""
+    return [int8_quantize(t, B) for t in tensors]
+
+
 def int8_gelu_forward(x, s_x, B):
     x2, bs = _flat(x); s2, _ = _flat(s_x)
     v = _deq(x2, s2, half_product=True)
