@@ -562,14 +562,15 @@ def run_gpt2(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    rec = gpt2_measure(args.model, args.micro_batch, args.steps, args.warmup, dev, rank, world, local, kernel_table=args.kernel_table)
+    rec = gpt2_measure(args.model, args.micro_batch, args.steps, args.warmup, dev, rank, world, local, kernel_table=args.kernel_table,
+                       bucket_mb=args.ddp_bucket_mb, bucket_view=not args.ddp_copy_grads)
     if rank == 0:
         print(json.dumps(rec), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local, kernel_table=False):
+def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local, kernel_table=False, bucket_mb=100, bucket_view=True):
     """One GPT-2 INT8 data-parallel training measurement (the process group, if any, is already initialised).  Returns the
     record on every rank (timing = max over ranks of the CUDA-event time)."""
     import torch
@@ -592,7 +593,9 @@ def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local
     nodecay = [p for p in model.parameters() if p.dim() < 2]
     # gradient clipping (max norm 1.0) + AdamW in one call; it re-points the parameters into one flat buffer, so before DDP
     opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=6e-4, betas=(0.9, 0.95), max_norm=1.0)
-    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    # gradients as views of DDP's buckets: no copy into and out of the buckets (the optimiser reads the gradients where they lie)
+    net = (torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=bucket_mb,
+                                                     gradient_as_bucket_view=bucket_view) if world > 1 else model)
     g = torch.Generator(device=dev).manual_seed(rank)
     T = cfg.block_size
 
@@ -883,6 +886,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (kernel tuning runs)")
     ap.add_argument("--no-extras", action="store_true", help="linear workload: skip the gpt2 and nonlinear records")
     ap.add_argument("--kernel-table", action="store_true", help="gpt2 workload: also print the device time per kernel")
+    ap.add_argument("--ddp-bucket-mb", type=int, default=100, help="gpt2 workload, N > 1: DDP bucket size")
+    ap.add_argument("--ddp-copy-grads", action="store_true", help="gpt2 workload, N > 1: DDP copies gradients through its buckets")
     ap.add_argument("--op", default=None, help="nonlinear workload: run only this operator (profiling)")
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--cols", type=int, default=3072)
