@@ -107,3 +107,10 @@ def test_sr_noise_mode_switch():
     assert prev == "philox" and NL.set_sr_noise(prev) == "torch"
     with pytest.raises(ValueError):
         NL.set_sr_noise("curand")
+
+
+def test_clip_adamw_refuses_cpu_parameters():
+    """No CPU path: the optimiser step only exists as a CUDA kernel."""
+    from jetfire_int8training_b200.optim import ClipAdamW
+    with pytest.raises(ValueError):
+        ClipAdamW([([torch.nn.Parameter(torch.zeros(8))], 0.0)], lr=1e-3)
