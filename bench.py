@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the Jetfire INT8 hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload linear|nonlinear|gpt2|gemm_sweep]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload linear|nonlinear|gpt2|gemm_sweep|optim]
 
 Default workload ("linear"): one per-block (32x32) INT8 linear layer at the headline GEMM shape M = N = K = 8192 --
 forward Y = X W^T, input gradient dX = dY W (stochastic rounding) and weight gradient dW = dY^T X -- i.e. three GEMM
@@ -781,6 +781,39 @@ def run_reference_gemm_sweep(args):
                       "shape": "kernel-level M x N x K", "shapes": out}), flush=True)
 
 
+def run_optim(args):
+    """Secondary workload: the fused clip + AdamW step on parameters with the shapes of GPT-2 124M (random gradients).
+    Prints ms per step and the HBM rate of its two passes (4 and 28 bytes per parameter)."""
+    import torch
+    from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
+    from jetfire_int8training_b200.optim import ClipAdamW
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = read_peaks()
+    model = QGPT(GPTConfig()).to(dev)
+    decay = [p for p in model.parameters() if p.dim() >= 2]
+    nodecay = [p for p in model.parameters() if p.dim() < 2]
+    opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=6e-4, betas=(0.9, 0.95), max_norm=1.0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    for p in opt.params:
+        p.grad = torch.randn(p.shape, generator=g, device=dev) * 1e-2
+    n = sum(p.numel() for p in opt.params)
+    for _ in range(max(3, args.warmup)):
+        opt.step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        out = opt.step()
+    b.record(); torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    gbs = 32.0 * n / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "clip + AdamW step", "parameters": n, "tensors": len(opt.params), "ms_per_step": ms,
+                      "bytes_per_parameter": 32, "GBps": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                      "grad_norm": float(out[0]), "applied_factor": float(out[1]),
+                      "note": "parameters, moments and gradients are 2 GB together, larger than L2"}), flush=True)
+
+
 def run_reference_nonlinear(args):
     """`--impl reference --workload nonlinear`: the reference's OWN nonlinear operators (the Triton kernels of Jetfire/Nonlinear,
     unmodified, compiled by the installed Triton with their full autotuning search) timed on this GPU through their public Python
@@ -882,7 +915,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear", "gpt2", "gemm_sweep"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "nonlinear", "gpt2", "gemm_sweep", "optim"])
     ap.add_argument("--model", default="124M", choices=["124M", "xl", "tiny"], help="gpt2 workload: model size")
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the linear workload")
@@ -905,6 +938,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "nonlinear":
         run_nonlinear(args)
+    elif args.workload == "optim":
+        run_optim(args)
     elif args.workload == "gpt2":
         run_gpt2(args)
     elif args.workload == "gemm_sweep":
