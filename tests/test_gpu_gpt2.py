@@ -55,6 +55,47 @@ def test_small_gpt2_trains():
     assert float(loss) < 0.7 * first
 
 
+def test_training_with_the_fused_optimiser_step_tracks_torch_adamw():
+    """The same tiny model trained twice from the same weights on the same batch with the same stochastic-rounding keys: once
+    with clip_grad_norm_ + torch.optim.AdamW, once with optim.ClipAdamW (which also has to invalidate the quantised-weight cache
+    through the parameters' version counters -- a stale cache would freeze the forward pass and the loss would stop moving)."""
+    from jetfire_int8training_b200 import rng
+    from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
+    from jetfire_int8training_b200.optim import ClipAdamW
+    cfg = GPTConfig(block_size=64, vocab_size=512, n_layer=2, n_head=4, n_embd=128)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (4, 65), generator=g, device=DEV)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    curves = []
+    for fused in (False, True):
+        torch.manual_seed(0)
+        rng.manual_seed(0)
+        model = QGPT(cfg).to(DEV)
+        decay = [p for p in model.parameters() if p.dim() >= 2]
+        nodecay = [p for p in model.parameters() if p.dim() < 2]
+        if fused:
+            opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=3e-3, betas=(0.9, 0.95), max_norm=1.0)
+        else:
+            opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": nodecay, "weight_decay": 0.0}], lr=3e-3,
+                                    betas=(0.9, 0.95))
+        losses = []
+        for _ in range(30):
+            loss = model(x, y)
+            loss.backward()
+            if not fused:
+                torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            losses.append(float(loss))
+        curves.append(losses)
+    a, b = curves
+    print("loss with torch AdamW / with ClipAdamW:", [round(v, 4) for v in a[::5]], [round(v, 4) for v in b[::5]])
+    assert b[-1] < 0.8 * b[0]                                          # it trains
+    assert abs(a[0] - b[0]) < 1e-6                                      # same start
+    for u, v in zip(a, b):                                              # same trajectory (the INT8 rounding amplifies last-bit
+        assert abs(u - v) < 0.02 * u                                    # differences of the update, so not bit for bit)
+
+
 def test_quantised_weights_are_cached_until_the_parameter_changes():
     from jetfire_int8training_b200 import Nonlinear as NL
     from jetfire_int8training_b200.gpt2 import quantized_weight
