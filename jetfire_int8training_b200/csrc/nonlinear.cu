@@ -402,7 +402,7 @@ quantize_kernel(const T* __restrict__ x, int64_t M, int64_t N, int8_t* __restric
 // dequantize: y = fp32(fp16(q) * s).  Pure data movement with a 1 : 4 size ratio between input and output, so the lane mapping
 // is chosen for the fp32 side: a thread owns one 4-byte word of payload (4 elements) per row and writes one float4; a CTA of 128
 // threads covers 32 rows x 512 columns = one row of 16 quantisation blocks, so the scale is loaded once per thread and every
-// warp access is a whole contiguous segment (128 B of payload, 512 B of output).  Eight rows are in flight per thread.
+// warp access is a whole contiguous segment (128 B of payload, 512 B of output).  All 32 rows are in flight per thread.
 // =========================================================================================================
 constexpr int DQ_THREADS = 128;
 
@@ -415,19 +415,19 @@ dequantize_kernel(const int8_t* __restrict__ q, const __half* __restrict__ s, in
     const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
     const int8_t* src = q + row0 * N + col;
     float* dst = y + row0 * N + col;
+    // all 32 rows of the thread's column word are requested before the first one is used (128 bytes in flight per thread: a CTA
+    // covers only 16 KB of payload, and small tensors put few CTAs on an SM)
+    uint32_t w[QB];
 #pragma unroll
-    for (int r0 = 0; r0 < QB; r0 += 8) {
-        uint32_t w[8];
+    for (int r = 0; r < QB; ++r)       // (volatile asm: the compiler otherwise sinks each load to its use and keeps few in flight)
+        asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w[r]) : "l"(src + (int64_t)r * N));
 #pragma unroll
-        for (int r = 0; r < 8; ++r) w[r] = __ldg(reinterpret_cast<const uint32_t*>(src + (int64_t)(r0 + r) * N));
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const uint32_t wx = w[r] ^ 0x80808080u;
-            const uint32_t lo = __byte_perm(wx, 0x64646464u, 0x5140), hi = __byte_perm(wx, 0x64646464u, 0x5342);
-            const float2 a = __half22float2(__hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&lo), bias), s2));
-            const float2 b = __half22float2(__hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&hi), bias), s2));
-            __stcs(reinterpret_cast<float4*>(dst + (int64_t)(r0 + r) * N), make_float4(a.x, a.y, b.x, b.y));   // written once, read by a later kernel
-        }
+    for (int r = 0; r < QB; ++r) {
+        const uint32_t wx = w[r] ^ 0x80808080u;
+        const uint32_t lo = __byte_perm(wx, 0x64646464u, 0x5140), hi = __byte_perm(wx, 0x64646464u, 0x5342);
+        const float2 a = __half22float2(__hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&lo), bias), s2));
+        const float2 b = __half22float2(__hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&hi), bias), s2));
+        __stcs(reinterpret_cast<float4*>(dst + (int64_t)r * N), make_float4(a.x, a.y, b.x, b.y));   // written once, read by a later kernel
     }
 }
 
