@@ -596,7 +596,8 @@ def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local
     decay = [p for p in model.parameters() if p.dim() >= 2]
     nodecay = [p for p in model.parameters() if p.dim() < 2]
     # gradient clipping (max norm 1.0) + AdamW in one call; it re-points the parameters into one flat buffer, so before DDP
-    opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=6e-4, betas=(0.9, 0.95), max_norm=1.0)
+    # (loss scale as the reference's GradScaler: init_scale 2^24, INT8_GPT2/train.py:217; halved while gradients overflow)
+    opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=6e-4, betas=(0.9, 0.95), max_norm=1.0, loss_scale=2.0 ** 24)
     # gradients as views of DDP's buckets: no copy into and out of the buckets (the optimiser reads the gradients where they lie)
     net = (torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=bucket_mb,
                                                      gradient_as_bucket_view=bucket_view) if world > 1 else model)
@@ -609,7 +610,7 @@ def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local
 
     def step(x, y):
         loss = net(x, y)
-        loss.backward()
+        opt.scale_loss(loss).backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
         return loss
@@ -635,7 +636,8 @@ def gpt2_measure(model_name, micro_batch, steps, warmup, dev, rank, world, local
            "dtype": "int8 linears/LN/GELU, bf16 attention + LM head, fp32 params", "data": "synthetic",
            "config": {"workload": f"GPT-2 {model_name} INT8 training step", "model": model_name, "n_layer": cfg.n_layer,
                       "n_embd": cfg.n_embd, "micro_batch": mb, "seq_len": T, "params": model.num_params(), "parallelism": f"dp{world}"},
-           "loss_first": losses[0], "loss_last": float(loss), "gemm_error_flag": err}
+           "loss_first": losses[0], "loss_last": float(loss), "gemm_error_flag": err,
+           "loss_scale": float(opt.state[0]), "optimizer_steps_taken": opt.step_count, "optimizer_steps_called": max(3, warmup) + steps}
     if kernel_table and rank == 0:
         # device time per kernel over three more steps (torch.profiler, CUDA activity), largest first
         from torch.profiler import ProfilerActivity, profile

@@ -214,23 +214,29 @@ int jf_lm_loss_backward(void* logits_bf16, const int64_t* targets, const float* 
                         int64_t rows, int64_t V, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------
- * Optimiser step of the caller (the un-quantised tail):  torch.nn.utils.clip_grad_norm_(params, max_norm) followed by
- * torch.optim.AdamW.step() of INT8_GPT2/train.py:320-329, as one entry point that reads every gradient twice and the optimiser
- * state once and never writes the clipped gradients.
+ * Optimiser step of the caller (the un-quantised tail):  scaler.unscale_(optimizer); clip_grad_norm_(params, max_norm);
+ * scaler.step(optimizer); scaler.update()  of INT8_GPT2/train.py:320-329 (AdamW, torch's GradScaler), as one entry point that reads
+ * every gradient twice and the optimiser state once and never writes the unscaled or clipped gradients.
  * Parameters, first and second moments are three flat fp32 device buffers of `total_chunks * jf_adamw_chunk_elements()` floats in
  * which tensor t occupies the elements starting at start_chunk[t] * jf_adamw_chunk_elements(); segments are back to back
  * (start_chunk[t+1] = start_chunk[t] + ceil(numel[t] / chunk)), numel[t] is a multiple of 4.  grads[t] is the device address of
  * tensor t's fp32 gradient (contiguous, 16-byte aligned).  `grads`, `numel`, `start_chunk`, `weight_decay` are HOST arrays of
- * n_tensors entries (copied into kernel parameters).  `step` is the 1-based step count of the bias corrections.  max_norm <= 0
- * disables clipping.  `partial` is a device workspace of total_chunks floats; `norm_coef` receives two device floats: the global
- * gradient norm and the factor the gradients were multiplied by, min(1, max_norm / (norm + 1e-6)).
+ * n_tensors entries (copied into kernel parameters).  max_norm <= 0 disables clipping.  `partial` is a device workspace of
+ * total_chunks floats.
+ * `state` is 8 device floats owned by the caller, read and updated by the call:
+ *   [0] loss scale (the gradients are scale x the true gradients; the caller multiplies its loss by this value; initialise to 1
+ *       for training without loss scaling), [1] steps since the scale last changed, [2] optimiser steps taken (initialise 0; the
+ *       bias corrections use it), [3] 1 if this call found a non-finite gradient and therefore changed nothing but the scale
+ *       (scale *= backoff_factor), [4] norm of the true gradients, [5] factor the raw gradients were multiplied by
+ *       (min(1, max_norm / (norm + 1e-6)) / scale), [6], [7] scratch.
+ * After growth_interval consecutive good steps the scale is multiplied by growth_factor (growth_interval = 0: never).
  * Arithmetic is fp32 with the expressions of torch.optim.AdamW (scalar factors formed in double and rounded once, as torch does);
  * results agree with torch to rounding (the norm is summed in a different, fixed, order). */
 int64_t jf_adamw_chunk_elements(void);
 int jf_adamw_clip_step(int64_t n_tensors, const void* const* grads, const int64_t* numel, const int64_t* start_chunk,
                        const float* weight_decay, float* params_flat, float* m_flat, float* v_flat, int64_t total_chunks,
-                       double lr, double beta1, double beta2, double eps, int64_t step, double max_norm, float* partial,
-                       float* norm_coef, void* stream);
+                       double lr, double beta1, double beta2, double eps, double max_norm, float* state, int64_t growth_interval,
+                       double growth_factor, double backoff_factor, float* partial, void* stream);
 
 #ifdef __cplusplus
 }

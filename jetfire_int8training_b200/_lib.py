@@ -41,7 +41,7 @@ SIGNATURES = {
     "jf_lm_loss_backward": ([_vp, _vp, _vp, _vp, ctypes.c_float, _i64, _i64, _vp], _int),
     "jf_adamw_chunk_elements": ([], _i64),
     "jf_adamw_clip_step": ([_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, ctypes.c_double, ctypes.c_double, ctypes.c_double,
-                            ctypes.c_double, _i64, ctypes.c_double, _vp, _vp, _vp], _int),
+                            ctypes.c_double, ctypes.c_double, _vp, _i64, ctypes.c_double, ctypes.c_double, _vp, _vp], _int),
 }
 
 _lib = None

@@ -4,12 +4,20 @@
 // INT8_GPT2/train.py:320-329).  With framework operators that is: one norm kernel per tensor, a norm of norms, a scaling pass that
 // reads and writes every gradient, and the optimiser pass -- 36 bytes per parameter through HBM and a few hundred launches.  Here:
 //   pass 1: sum of squares of every gradient (read 4 B / parameter), one partial per 4096-element chunk, reduced in a fixed order;
-//   pass 2: p, m, v <- AdamW(p, m, v, g * coef) with coef = min(1, max_norm / (norm + 1e-6)) read from device memory
+//   pass 2: p, m, v <- AdamW(p, m, v, g * coef) with coef = min(1, max_norm / (norm + 1e-6)) / loss scale, read from device memory
 //           (read 16 B, write 12 B / parameter) -- the clipped gradient is never written.
 // Parameters, first and second moments live in three flat fp32 buffers in which tensor t occupies elements
 // [4096 * start_chunk[t], 4096 * start_chunk[t] + numel[t]); the gradients stay where autograd put them and are passed as a pointer
 // per tensor.  The per-tensor tables travel in the kernel parameters (at most ADAMW_MAX_TENSORS per launch; the host entry point
 // loops).  A CTA owns one chunk and finds its tensor by bisection over start_chunk.
+//
+// Loss scaling (the reference trains in fp16 with torch's GradScaler, init_scale 2^24: INT8_GPT2/train.py:216-217, 320-327): the
+// gradients arrive multiplied by the loss scale.  Its state lives in device memory (`state`, 8 floats: [0] scale, [1] steps since
+// the scale last changed, [2] optimiser steps taken, [3] 1 if this call found a non-finite gradient, [4] norm of the unscaled
+// gradients, [5] factor applied to the raw gradients = clip factor / scale, [6] lr / (1 - beta1^t), [7] sqrt(1 - beta2^t)): the
+// one-CTA kernel between the two passes unscales the norm, decides whether the step is skipped (non-finite gradients: scale *=
+// backoff, nothing else changes) and grows the scale after `growth_interval` good steps, as GradScaler does -- without a host
+// synchronisation.  scale = 1 with growth_interval = 0 is plain training without loss scaling.
 //
 // Arithmetic (fp32, the same expressions as torch.optim.AdamW, whose scalar factors are formed in double precision on the host and
 // rounded to fp32 once): p *= 1 - lr * wd;  m += (g - m) * (1 - beta1);  v = beta2 * v + (1 - beta2) * g * g;
@@ -68,9 +76,14 @@ __global__ void __launch_bounds__(ADAMW_THREADS) grad_sumsq_kernel(const AdamwTe
     }
 }
 
-// out[0] = sqrt(sum of the partials), out[1] = min(1, max_norm / (out[0] + 1e-6))   (max_norm <= 0: no clipping, out[1] = 1)
-__global__ void __launch_bounds__(1024) grad_norm_finish_kernel(const float* __restrict__ partial, int64_t count, float max_norm,
-                                                               float* __restrict__ out) {
+struct AdamwScalars {
+    double lr, beta1, beta2, max_norm, growth_factor, backoff_factor;
+    int64_t growth_interval;      // 0: the scale never grows
+};
+
+// One CTA: global norm from the partials, loss-scale bookkeeping, and the per-step scalars of the update (see `state` above).
+__global__ void __launch_bounds__(1024) grad_norm_finish_kernel(const float* __restrict__ partial, int64_t count, const AdamwScalars h,
+                                                               float* __restrict__ state) {
     __shared__ double red[1024];
     double a = 0.0;
     for (int64_t i = threadIdx.x; i < count; i += 1024) a += (double)partial[i];
@@ -81,21 +94,42 @@ __global__ void __launch_bounds__(1024) grad_norm_finish_kernel(const float* __r
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        const float norm = (float)sqrt(red[0]);
-        out[0] = norm;
-        out[1] = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+        const double sumsq = red[0];
+        const float scale = state[0];
+        const bool bad = !isfinite(sumsq) || !(scale > 0.f);
+        state[3] = bad ? 1.f : 0.f;
+        if (bad) {
+            state[0] = (float)((double)scale * h.backoff_factor);
+            state[1] = 0.f;
+            state[4] = (float)sqrt(sumsq) / scale;
+            state[5] = 0.f;
+            return;
+        }
+        const float norm = (float)(sqrt(sumsq) / (double)scale);
+        const float clip = h.max_norm > 0.0 ? fminf(1.f, (float)h.max_norm / (norm + 1e-6f)) : 1.f;
+        const double step = (double)state[2] + 1.0;
+        state[2] = (float)step;
+        state[4] = norm;
+        state[5] = clip / scale;
+        state[6] = (float)(h.lr / (1.0 - pow(h.beta1, step)));
+        state[7] = (float)sqrt(1.0 - pow(h.beta2, step));
+        float tracker = state[1] + 1.f;
+        if (h.growth_interval > 0 && tracker >= (float)h.growth_interval) {
+            state[0] = (float)((double)scale * h.growth_factor);
+            tracker = 0.f;
+        }
+        state[1] = tracker;
     }
 }
 
 struct AdamwHyper {
     float one_minus_beta1, beta2, one_minus_beta2, eps;
-    float step_size;        // lr / (1 - beta1^step)
-    float sqrt_bc2;         // sqrt(1 - beta2^step)
 };
 
 __global__ void __launch_bounds__(ADAMW_THREADS) adamw_kernel(const AdamwTensors ts, int64_t first_chunk, float* __restrict__ p_flat,
                                                              float* __restrict__ m_flat, float* __restrict__ v_flat,
-                                                             const float* __restrict__ norm_coef, const AdamwHyper h) {
+                                                             const float* __restrict__ state, const AdamwHyper h) {
+    if (__ldg(state + 3) != 0.f) return;      // non-finite gradients: the step is skipped
     const int t = find_tensor(ts, (int)blockIdx.x);
     const int off = ((int)blockIdx.x - ts.start_chunk[t]) * ADAMW_CHUNK;
     const int n = min(ADAMW_CHUNK, ts.numel[t] - off);
@@ -104,7 +138,7 @@ __global__ void __launch_bounds__(ADAMW_THREADS) adamw_kernel(const AdamwTensors
     float4* p4 = reinterpret_cast<float4*>(p_flat + base);
     float4* m4 = reinterpret_cast<float4*>(m_flat + base);
     float4* v4 = reinterpret_cast<float4*>(v_flat + base);
-    const float coef = __ldg(norm_coef + 1);
+    const float coef = __ldg(state + 5), step_size = __ldg(state + 6), sqrt_bc2 = __ldg(state + 7);
     const float decay = ts.decay[t];
     const float omb1 = h.one_minus_beta1, omb2 = h.one_minus_beta2;
 #pragma unroll
@@ -120,8 +154,8 @@ __global__ void __launch_bounds__(ADAMW_THREADS) adamw_kernel(const AdamwTensors
             p[j] *= decay;
             m[j] += (g[j] - m[j]) * omb1;
             v[j] = h.beta2 * v[j] + omb2 * g[j] * g[j];
-            const float denom = __fdiv_rn(__fsqrt_rn(v[j]), h.sqrt_bc2) + h.eps;
-            p[j] -= h.step_size * __fdiv_rn(m[j], denom);
+            const float denom = __fdiv_rn(__fsqrt_rn(v[j]), sqrt_bc2) + h.eps;
+            p[j] -= step_size * __fdiv_rn(m[j], denom);
         }
         p4[i] = make_float4(p[0], p[1], p[2], p[3]);
         m4[i] = make_float4(m[0], m[1], m[2], m[3]);
@@ -139,10 +173,10 @@ int64_t jf_adamw_chunk_elements(void) { return ADAMW_CHUNK; }
 
 int jf_adamw_clip_step(int64_t n_tensors, const void* const* grads, const int64_t* numel, const int64_t* start_chunk,
                        const float* weight_decay, float* params_flat, float* m_flat, float* v_flat, int64_t total_chunks,
-                       double lr, double beta1, double beta2, double eps, int64_t step, double max_norm, float* partial,
-                       float* norm_coef, void* stream) {
-    if (!grads || !numel || !start_chunk || !weight_decay || !params_flat || !m_flat || !v_flat || !partial || !norm_coef) return JF_ERR_NULL;
-    if (n_tensors <= 0 || total_chunks <= 0 || total_chunks >= (int64_t(1) << 31) || step <= 0) return JF_ERR_SHAPE;
+                       double lr, double beta1, double beta2, double eps, double max_norm, float* state, int64_t growth_interval,
+                       double growth_factor, double backoff_factor, float* partial, void* stream) {
+    if (!grads || !numel || !start_chunk || !weight_decay || !params_flat || !m_flat || !v_flat || !partial || !state) return JF_ERR_NULL;
+    if (n_tensors <= 0 || total_chunks <= 0 || total_chunks >= (int64_t(1) << 31) || growth_interval < 0) return JF_ERR_SHAPE;
     if (!aligned16(params_flat) || !aligned16(m_flat) || !aligned16(v_flat)) return JF_ERR_ALIGN;
     for (int64_t t = 0; t < n_tensors; ++t) {
         if (!grads[t]) return JF_ERR_NULL;
@@ -154,8 +188,9 @@ int jf_adamw_clip_step(int64_t n_tensors, const void* const* grads, const int64_
     cudaStream_t st = (cudaStream_t)stream;
     AdamwHyper h;
     h.one_minus_beta1 = (float)(1.0 - beta1); h.beta2 = (float)beta2; h.one_minus_beta2 = (float)(1.0 - beta2); h.eps = (float)eps;
-    h.step_size = (float)(lr / (1.0 - pow(beta1, (double)step)));
-    h.sqrt_bc2 = (float)sqrt(1.0 - pow(beta2, (double)step));
+    AdamwScalars sc;
+    sc.lr = lr; sc.beta1 = beta1; sc.beta2 = beta2; sc.max_norm = max_norm; sc.growth_factor = growth_factor;
+    sc.backoff_factor = backoff_factor; sc.growth_interval = growth_interval;
     // launches of at most ADAMW_MAX_TENSORS tensors; a launch covers exactly the chunks that hold numbers (the padding chunks
     // between two segments, if any, belong to no launch)
     auto for_groups = [&](auto&& launch) -> int {
@@ -185,10 +220,10 @@ int jf_adamw_clip_step(int64_t n_tensors, const void* const* grads, const int64_
     if (int e = for_groups([&](const AdamwTensors& ts, int64_t first, unsigned chunks) {
             grad_sumsq_kernel<<<chunks, ADAMW_THREADS, 0, st>>>(ts, first, partial);
         })) return e;
-    grad_norm_finish_kernel<<<1, 1024, 0, st>>>(partial, total_chunks, (float)max_norm, norm_coef);
+    grad_norm_finish_kernel<<<1, 1024, 0, st>>>(partial, total_chunks, sc, state);
     if (int e = check_launch()) return e;
     return for_groups([&](const AdamwTensors& ts, int64_t first, unsigned chunks) {
-        adamw_kernel<<<chunks, ADAMW_THREADS, 0, st>>>(ts, first, params_flat, m_flat, v_flat, norm_coef, h);
+        adamw_kernel<<<chunks, ADAMW_THREADS, 0, st>>>(ts, first, params_flat, m_flat, v_flat, state, h);
     });
 }
 

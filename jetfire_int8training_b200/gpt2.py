@@ -41,30 +41,26 @@ def _f8(t):
 
 
 def quantized_weight(w):
-    """(int8 payload, fp16 scales) of a weight matrix, cached on the parameter until the parameter changes.
-
-    The reference re-quantises every weight in every forward pass (INT8_GPT2/qmodel.py:92, 139, 199-200); with gradient
-    accumulation that is the same quantisation of the same values once per micro-step.  The cache key is the tensor's
-    version counter, which every in-place update (the optimiser step, a checkpoint load) advances, together with its storage
-    address; round-to-nearest quantisation is deterministic, so a cached result is bit-identical to a fresh one."""
-    key = (w._version, w.data_ptr())
-    hit = getattr(w, "_jf_qcache", None)
-    if hit is not None and hit[0] == key:
-        return hit[1], hit[2]
-    qw, sw = NL.int8_quantize(w.detach(), QB)
-    w._jf_qcache = (key, qw, sw)
-    return qw, sw
+    """(int8 payload, fp16 scales) of a weight matrix for the forward pass that is running: the pair that
+    quantise_weights() stored on the parameter at the start of this pass, else a fresh quantisation."""
+    hit = getattr(w, "_jf_q", None)
+    if hit is not None:
+        return hit
+    return NL.int8_quantize(w.detach(), QB)
 
 
-def refresh_weight_cache(weights):
-    """Quantise every weight of `weights` whose cached quantisation is stale, eight tensors per kernel launch, and store the
-    results where quantized_weight finds them.  After an optimiser step all 4*n_layer matrices of a model are stale: this
-    replaces that many launches (each smaller than one wave of the GPU at GPT-2 124M sizes) by n_layer/2."""
-    stale = [w for w in weights if getattr(w, "_jf_qcache", (None,))[0] != (w._version, w.data_ptr())]
-    if not stale:
+def quantise_weights(weights, reuse=False):
+    """Quantise the weight matrices of a model for one forward pass, eight tensors per kernel launch, and store the results
+    where quantized_weight finds them (the reference quantises each weight where it is used, INT8_GPT2/qmodel.py:92, 139,
+    199-200: 4 * n_layer launches, each smaller than one wave of the GPU at GPT-2 124M sizes).
+
+    `reuse=True` keeps the quantisations of the previous pass.  Only the caller knows that the weights have not changed since --
+    the further micro-steps of a gradient-accumulation step -- and has to say so: a parameter's version counter is NOT a safe
+    key, because fused optimisers (torch.optim.AdamW(fused=True)) update parameters without advancing it."""
+    if reuse and all(getattr(w, "_jf_q", None) is not None for w in weights):
         return
-    for w, (qw, sw) in zip(stale, NL.int8_quantize_many([w.detach() for w in stale], QB)):
-        w._jf_qcache = ((w._version, w.data_ptr()), qw, sw)
+    for w, pair in zip(weights, NL.int8_quantize_many([w.detach() for w in weights], QB)):
+        w._jf_q = pair
 
 
 def _i8(t):
@@ -221,11 +217,13 @@ class QGPT(nn.Module):
     def num_params(self):
         return sum(p.numel() for p in self.parameters()) - self.wpe.weight.numel()
 
-    def forward(self, idx, targets):
+    def forward(self, idx, targets, reuse_quantised_weights=False):
+        """`reuse_quantised_weights`: the weights have not changed since the previous forward pass (micro-steps 2.. of a
+        gradient-accumulation step), keep their quantisations."""
         B, T = idx.shape
         pos = torch.arange(T, device=idx.device)
         x = self.wte(idx) + self.wpe(pos)
-        refresh_weight_cache([w for b in self.blocks for w in (b.c_attn, b.c_proj, b.c_fc, b.c_proj2)])
+        quantise_weights([w for b in self.blocks for w in (b.c_attn, b.c_proj, b.c_fc, b.c_proj2)], reuse=reuse_quantised_weights)
         x, qx, sx = _Begin.apply(x)
         mean = x.mean(-1)
         rstd = 1.0 / x.var(-1).sqrt()

@@ -3,10 +3,11 @@ on the reference's INT8 recipe restated in plain torch (tests/torch_recipe.py, p
 kernels by tests/test_recipe_golden.py) -- same initial weights, same batches, same optimiser; only the stochastic-rounding noise
 streams differ.
 
-    python tests/loss_curve_124m.py [--steps 2000] [--micro-batch 12] [--layers 12] [--stream learnable|uniform] [--seed-variance]
+    python tests/loss_curve_124m.py [--steps 2000] [--micro-batch 12] [--layers 12] [--stream learnable|uniform] [--seed-variance | --compare-optimizers]
 
 GPT-2 124M: 12 layers, 12 heads, d = 768, context 1024, vocabulary 50304, AdamW lr 6e-4 (100 warm-up steps), betas (0.9, 0.95),
-weight decay 0.1, gradient clipping 1.0.  Token stream: seeded synthetic ids.  `uniform` draws them uniformly (nothing can be
+weight decay 0.1, gradient clipping 1.0, loss scaling as the reference's GradScaler (init 2^24; the fp16 gradients that cross the
+attention underflow without it).  Every forward pass quantises the current weights.  Token stream: seeded synthetic ids.  `uniform` draws them uniformly (nothing can be
 learnt: the curve stays at ln 50304); `learnable` (default) makes the next token (5 t + 17 + {0,1,2}) mod 50304, so the loss
 falls and a mismatch between the two implementations would show.  Prints one JSON line with the mean loss of every 100-step
 window for both runs and the largest relative gap between them.  --seed-variance runs the CUDA operators twice instead, with
@@ -60,26 +61,46 @@ def batches(steps, mb, T, vocab, stream, seed):
         yield ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
 
 
-def train(model, args, use_recipe):
+def train(model, args, use_recipe, fused_optimizer=False):
+    """Loss scaling as in the reference's loop (INT8_GPT2/train.py:216-217, 320-327): GradScaler(init_scale=2**24), unscale, clip
+    to norm 1.0, step, update.  Returns (losses, number of steps the scaler skipped)."""
     decay = [p for p in model.parameters() if p.dim() >= 2]
     nodecay = [p for p in model.parameters() if p.dim() < 2]
-    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": nodecay, "weight_decay": 0.0}], lr=6e-4,
-                            betas=(0.9, 0.95), fused=True)
+    if fused_optimizer:
+        from jetfire_int8training_b200.optim import ClipAdamW
+        opt = ClipAdamW([(decay, 0.1), (nodecay, 0.0)], lr=6e-4, betas=(0.9, 0.95), max_norm=1.0, loss_scale=2.0 ** 24)
+        scaler = None
+    else:
+        opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": nodecay, "weight_decay": 0.0}], lr=6e-4,
+                                betas=(0.9, 0.95), fused=True)
+        scaler = torch.amp.GradScaler("cuda", init_scale=2.0 ** 24)
     losses = []
     ctx = recipe_ops() if use_recipe else contextlib.nullcontext()
     t0 = time.time()
     with ctx:
         for i, (x, y) in enumerate(batches(args.steps, args.micro_batch, model.cfg.block_size, model.cfg.vocab_size, args.stream, 1234)):
-            for grp in opt.param_groups:
-                grp["lr"] = 6e-4 * min(1.0, (i + 1) / 100.0)
+            lr = 6e-4 * min(1.0, (i + 1) / 100.0)
+            if fused_optimizer:
+                opt.lr = lr
+            else:
+                for grp in opt.param_groups:
+                    grp["lr"] = lr
             loss = model(x, y)
             opt.zero_grad(set_to_none=True)
-            loss.backward()
-            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
-            opt.step()
+            if fused_optimizer:
+                opt.scale_loss(loss).backward()
+                opt.step()              # unscales, clips to norm 1.0, steps and updates the scale itself
+            else:
+                scaler.scale(loss).backward()
+                scaler.unscale_(opt)
+                torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+                scaler.step(opt)
+                scaler.update()
             losses.append(loss.detach())
             if (i + 1) % 100 == 0:
-                print(f"{'recipe' if use_recipe else 'cuda'} step {i + 1}: loss {float(losses[-1]):.4f}  ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+                sc = float(opt.state[0]) if fused_optimizer else scaler.get_scale()
+                print(f"{'recipe' if use_recipe else 'cuda'} step {i + 1}: loss {float(losses[-1]):.4f}  loss scale {sc:g}  ({time.time() - t0:.0f} s)",
+                      file=sys.stderr, flush=True)
     return torch.stack(losses).float().cpu()
 
 
@@ -90,6 +111,8 @@ def main():
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--stream", default="learnable", choices=["learnable", "uniform"])
     ap.add_argument("--seed-variance", action="store_true")
+    ap.add_argument("--compare-optimizers", action="store_true",
+                    help="CUDA operators twice, same stochastic-rounding seed: optim.ClipAdamW against clip_grad_norm_ + torch AdamW")
     args = ap.parse_args()
     from jetfire_int8training_b200 import rng
     from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
@@ -98,11 +121,14 @@ def main():
     cfg = GPTConfig(n_layer=args.layers)
     ours = QGPT(cfg).to(DEV)
     theirs = copy.deepcopy(ours)
-    a = train(ours, args, use_recipe=False)
+    a = train(ours, args, use_recipe=False, fused_optimizer=args.compare_optimizers)
     del ours
     torch.cuda.empty_cache()
     torch.manual_seed(1)
-    if args.seed_variance:
+    if args.compare_optimizers:
+        rng.manual_seed(0)                           # the same stochastic-rounding stream: only the optimiser step differs
+        b = train(theirs, args, use_recipe=False)
+    elif args.seed_variance:
         rng.manual_seed(12345)                       # a different stochastic-rounding stream, same weights and batches
         b = train(theirs, args, use_recipe=False)
     else:
@@ -111,7 +137,8 @@ def main():
     wins = [(round(float(a[i:i + w].mean()), 4), round(float(b[i:i + w].mean()), 4)) for i in range(0, args.steps - w + 1, w)]
     gap = max(abs(x - y) / y for x, y in wins)
     print(json.dumps({"model": f"GPT-2 124M shape, {args.layers} layers", "steps": args.steps, "micro_batch": args.micro_batch, "stream": args.stream,
-                      "window": w, "compared": "cuda (SR seed 0) vs cuda (SR seed 12345)" if args.seed_variance else "cuda vs recipe",
+                      "window": w, "compared": ("cuda with optim.ClipAdamW vs cuda with clip_grad_norm_ + torch AdamW" if args.compare_optimizers else
+                                   "cuda (SR seed 0) vs cuda (SR seed 12345)" if args.seed_variance else "cuda vs recipe"),
                       "window_means_cuda_vs_recipe": wins, "max_relative_gap_of_window_means": gap,
                       "first_loss": [float(a[0]), float(b[0])], "last_window": wins[-1], "finite": bool(torch.isfinite(a).all() and torch.isfinite(b).all())}))
 

@@ -96,21 +96,31 @@ def test_training_with_the_fused_optimiser_step_tracks_torch_adamw():
         assert abs(u - v) < 0.02 * u                                    # differences of the update, so not bit for bit)
 
 
-def test_quantised_weights_are_cached_until_the_parameter_changes():
-    from jetfire_int8training_b200 import Nonlinear as NL
-    from jetfire_int8training_b200.gpt2 import quantized_weight
+def test_weights_are_quantised_every_forward_unless_the_caller_asks_for_reuse():
+    """A fused optimiser (torch.optim.AdamW(fused=True)) updates parameters WITHOUT advancing their version counters, so the
+    quantised weights must not be cached on that key: by default every forward pass quantises the current values; only an
+    explicit reuse_quantised_weights=True keeps the previous pass's."""
+    from jetfire_int8training_b200 import Nonlinear as NL, rng
+    from jetfire_int8training_b200.gpt2 import GPTConfig, QGPT
     torch.manual_seed(1)
-    w = torch.nn.Parameter(0.02 * torch.randn(256, 128, device=DEV))
-    q1, s1 = quantized_weight(w)
-    q2, s2 = quantized_weight(w)
-    assert q1 is q2 and s1 is s2                                        # second micro-step: no new quantisation
-    fresh_q, fresh_s = NL.int8_quantize(w.detach(), 32)
-    assert torch.equal(q1, fresh_q) and torch.equal(s1, fresh_s)
+    cfg = GPTConfig(block_size=64, vocab_size=512, n_layer=1, n_head=4, n_embd=128)
+    model = QGPT(cfg).to(DEV)
+    ids = torch.randint(0, cfg.vocab_size, (2, 65), device=DEV)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    w = model.blocks[0].c_fc
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2, fused=True)
+    rng.manual_seed(0)
+    model(x, y).backward()
+    q_before = w._jf_q[0].clone()
+    opt.step()                                                           # in place, possibly without a version bump
+    opt.zero_grad(set_to_none=True)
     with torch.no_grad():
-        w.mul_(1.5)                                                     # what an optimiser step does: in place, version advances
-    q3, s3 = quantized_weight(w)
+        rng.manual_seed(0); l_reuse = float(model(x, y, reuse_quantised_weights=True))
+        assert torch.equal(w._jf_q[0], q_before)                          # asked for: the previous quantisation is kept
+        rng.manual_seed(0); l_fresh = float(model(x, y))
     fresh_q, fresh_s = NL.int8_quantize(w.detach(), 32)
-    assert q3 is not q1 and torch.equal(q3, fresh_q) and torch.equal(s3, fresh_s)
+    assert torch.equal(w._jf_q[0], fresh_q) and torch.equal(w._jf_q[1], fresh_s)     # default: the updated values
+    assert not torch.equal(fresh_q, q_before) and l_fresh != l_reuse
 
 
 @pytest.mark.parametrize("rows,V", [(64, 512), (96, 50304), (33, 1000)])

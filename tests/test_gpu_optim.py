@@ -52,6 +52,44 @@ def test_clip_adamw_matches_torch(case):
             torch.testing.assert_close(mine, theirs, rtol=2e-6, atol=2e-7 * float(theirs.abs().max()))
 
 
+def test_loss_scale_unscales_skips_and_grows():
+    """GradScaler's rule on the device: scaled gradients give the same update as unscaled ones; a non-finite gradient skips the
+    step and halves the scale; growth_interval good steps in a row double it."""
+    from jetfire_int8training_b200.optim import ClipAdamW
+    shapes = [(256, 128), (128,), (4100,)]
+    ours, ref = _make(shapes, 5), _make(shapes, 5)
+    opt = ClipAdamW([(ours, 0.1)], lr=1e-3, max_norm=1.0, loss_scale=1024.0, growth_interval=2)
+    topt = torch.optim.AdamW(ref, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    gen = torch.Generator().manual_seed(6)
+    scales = []
+    for step in range(5):
+        poison = step == 2
+        scale = float(opt.state[0])
+        for a, b in zip(ours, ref):
+            gr = torch.randn(a.shape, generator=gen).to(DEV)
+            a.grad = gr * scale
+            b.grad = gr.clone()
+        if poison:
+            ours[1].grad[7] = float("inf")
+        before = [p.detach().clone() for p in ours]
+        out = opt.step()
+        if poison:
+            assert float(out[2]) == 1.0 and all(torch.equal(p.data, q) for p, q in zip(ours, before))     # nothing changed ...
+            assert float(opt.state[0]) == scale * 0.5                                                      # ... but the scale
+        else:
+            assert float(out[2]) == 0.0
+            tn = torch.nn.utils.clip_grad_norm_(ref, 1.0)
+            topt.step()
+            assert abs(float(out[0]) - float(tn)) <= 1e-5 * float(tn)
+            for a, b in zip(ours, ref):
+                torch.testing.assert_close(a.data, b.data, rtol=2e-6, atol=1e-7)
+        scales.append(float(opt.state[0]))
+    assert scales == [1024.0, 2048.0, 1024.0, 1024.0, 2048.0]
+    assert opt.step_count == 4                                            # the skipped step does not count
+    loss = torch.ones((), device=DEV, requires_grad=True)
+    assert float(opt.scale_loss(loss)) == 2048.0
+
+
 def test_parameters_become_views_of_one_buffer():
     from jetfire_int8training_b200.optim import ClipAdamW
     ps = _make([(8, 8), (4,)], 3)
