@@ -10,7 +10,7 @@ in floating point, as they do in the reference.
 
 Differences from the reference's module, none of which touch the operators' semantics: weight gradients are produced in fp32
 (the reference's fp16 overflows under its 2^24 loss scale), the materialised dY^T copies are not made (the GEMMs read dY
-in place), and a weight is quantised once per value (cached until the optimiser changes it) instead of once per forward pass.
+in place), and the weight matrices are quantised eight per kernel launch at the start of the forward pass.
 """
 import math
 from dataclasses import dataclass

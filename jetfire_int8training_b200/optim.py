@@ -95,7 +95,7 @@ class ClipAdamW:
                                        self._partial.data_ptr(), torch.cuda.current_stream().cuda_stream), "adamw_clip_step")
         out = self.state[[4, 5, 3]]
         # the parameters were updated in place through the flat buffer by a kernel autograd does not know about: advance their
-        # version counters (what an in-place torch operation would have done; caches keyed on the version see the change)
+        # version counters (what an in-place torch operation would have done)
         torch.autograd.graph.increment_version(self.params)
         return out
 
