@@ -226,9 +226,9 @@ int jf_lm_loss_backward(void* logits_bf16, const int64_t* targets, const float* 
  * `state` is 8 device floats owned by the caller, read and updated by the call:
  *   [0] loss scale (the gradients are scale x the true gradients; the caller multiplies its loss by this value; initialise to 1
  *       for training without loss scaling), [1] steps since the scale last changed, [2] optimiser steps taken (initialise 0; the
- *       bias corrections use it), [3] 1 if this call found a non-finite gradient and therefore changed nothing but the scale
- *       (scale *= backoff_factor), [4] norm of the true gradients, [5] factor the raw gradients were multiplied by
- *       (min(1, max_norm / (norm + 1e-6)) / scale), [6], [7] scratch.
+ *       bias corrections use it), [3] norm of the true gradients, [4] factor the raw gradients were multiplied by
+ *       (min(1, max_norm / (norm + 1e-6)) / scale), [5] 1 if this call found a non-finite gradient and therefore changed nothing
+ *       but the scale (scale *= backoff_factor), [6], [7] scratch.
  * After growth_interval consecutive good steps the scale is multiplied by growth_factor (growth_interval = 0: never).
  * Arithmetic is fp32 with the expressions of torch.optim.AdamW (scalar factors formed in double and rounded once, as torch does);
  * results agree with torch to rounding (the norm is summed in a different, fixed, order). */

@@ -13,8 +13,8 @@
 //
 // Loss scaling (the reference trains in fp16 with torch's GradScaler, init_scale 2^24: INT8_GPT2/train.py:216-217, 320-327): the
 // gradients arrive multiplied by the loss scale.  Its state lives in device memory (`state`, 8 floats: [0] scale, [1] steps since
-// the scale last changed, [2] optimiser steps taken, [3] 1 if this call found a non-finite gradient, [4] norm of the unscaled
-// gradients, [5] factor applied to the raw gradients = clip factor / scale, [6] lr / (1 - beta1^t), [7] sqrt(1 - beta2^t)): the
+// the scale last changed, [2] optimiser steps taken, [3] norm of the unscaled gradients, [4] factor applied to the raw gradients =
+// clip factor / scale, [5] 1 if this call found a non-finite gradient, [6] lr / (1 - beta1^t), [7] sqrt(1 - beta2^t)): the
 // one-CTA kernel between the two passes unscales the norm, decides whether the step is skipped (non-finite gradients: scale *=
 // backoff, nothing else changes) and grows the scale after `growth_interval` good steps, as GradScaler does -- without a host
 // synchronisation.  scale = 1 with growth_interval = 0 is plain training without loss scaling.
@@ -97,20 +97,20 @@ __global__ void __launch_bounds__(1024) grad_norm_finish_kernel(const float* __r
         const double sumsq = red[0];
         const float scale = state[0];
         const bool bad = !isfinite(sumsq) || !(scale > 0.f);
-        state[3] = bad ? 1.f : 0.f;
+        state[5] = bad ? 1.f : 0.f;
         if (bad) {
             state[0] = (float)((double)scale * h.backoff_factor);
             state[1] = 0.f;
-            state[4] = (float)sqrt(sumsq) / scale;
-            state[5] = 0.f;
+            state[3] = (float)sqrt(sumsq) / scale;
+            state[4] = 0.f;
             return;
         }
         const float norm = (float)(sqrt(sumsq) / (double)scale);
         const float clip = h.max_norm > 0.0 ? fminf(1.f, (float)h.max_norm / (norm + 1e-6f)) : 1.f;
         const double step = (double)state[2] + 1.0;
         state[2] = (float)step;
-        state[4] = norm;
-        state[5] = clip / scale;
+        state[3] = norm;
+        state[4] = clip / scale;
         state[6] = (float)(h.lr / (1.0 - pow(h.beta1, step)));
         state[7] = (float)sqrt(1.0 - pow(h.beta2, step));
         float tracker = state[1] + 1.f;
@@ -129,7 +129,7 @@ struct AdamwHyper {
 __global__ void __launch_bounds__(ADAMW_THREADS) adamw_kernel(const AdamwTensors ts, int64_t first_chunk, float* __restrict__ p_flat,
                                                              float* __restrict__ m_flat, float* __restrict__ v_flat,
                                                              const float* __restrict__ state, const AdamwHyper h) {
-    if (__ldg(state + 3) != 0.f) return;      // non-finite gradients: the step is skipped
+    if (__ldg(state + 5) != 0.f) return;      // non-finite gradients: the step is skipped
     const int t = find_tensor(ts, (int)blockIdx.x);
     const int off = ((int)blockIdx.x - ts.start_chunk[t]) * ADAMW_CHUNK;
     const int n = min(ADAMW_CHUNK, ts.numel[t] - off);
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(ADAMW_THREADS) adamw_kernel(const AdamwTensors
     float4* p4 = reinterpret_cast<float4*>(p_flat + base);
     float4* m4 = reinterpret_cast<float4*>(m_flat + base);
     float4* v4 = reinterpret_cast<float4*>(v_flat + base);
-    const float coef = __ldg(state + 5), step_size = __ldg(state + 6), sqrt_bc2 = __ldg(state + 7);
+    const float coef = __ldg(state + 4), step_size = __ldg(state + 6), sqrt_bc2 = __ldg(state + 7);
     const float decay = ts.decay[t];
     const float omb1 = h.one_minus_beta1, omb2 = h.one_minus_beta2;
 #pragma unroll

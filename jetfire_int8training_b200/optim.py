@@ -61,7 +61,7 @@ class ClipAdamW:
         self._wd = (ctypes.c_float * n)(*wds)
         self._partial = torch.empty(c, dtype=torch.float32, device=dev)
         self._GradArray = ctypes.c_void_p * n
-        # [scale, steps since the scale changed, optimiser steps taken, skipped, norm, applied factor, 2 x scratch]
+        # [scale, steps since the scale changed, optimiser steps taken, norm, applied factor, skipped, 2 x scratch]
         self.state = torch.zeros(8, dtype=torch.float32, device=dev)
         self.state[0] = 1.0 if loss_scale is None else float(loss_scale)
 
@@ -93,7 +93,7 @@ class ClipAdamW:
                                        self.total_chunks, self.lr, self.betas[0], self.betas[1], self.eps, self.max_norm,
                                        self.state.data_ptr(), self.growth_interval, self.growth_factor, self.backoff_factor,
                                        self._partial.data_ptr(), torch.cuda.current_stream().cuda_stream), "adamw_clip_step")
-        out = self.state[[4, 5, 3]]
+        out = self.state[3:6].clone()          # [gradient norm, applied factor, skipped]
         # the parameters were updated in place through the flat buffer by a kernel autograd does not know about: advance their
         # version counters (what an in-place torch operation would have done)
         torch.autograd.graph.increment_version(self.params)
