@@ -558,7 +558,8 @@ def nonlinear_measure(dev, steps, warmup):
 
 def run_gpt2(args):
     """GPT-2 INT8 training step (nanoGPT shape, synthetic uniform token ids): forward + backward through the INT8 data flow,
-    gradient all-reduce (DDP over NCCL when n_gpus > 1) and a fused AdamW step.  Prints tokens/s."""
+    gradient all-reduce (DDP over NCCL when n_gpus > 1) and the fused loss-scale + clip + AdamW step (optim.ClipAdamW, loss scale
+    from 2^24 as the reference's GradScaler).  Prints tokens/s."""
     import torch
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
