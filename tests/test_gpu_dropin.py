@@ -77,6 +77,22 @@ def test_reference_qmodel_runs_unmodified_on_this_package(installed):
             b.ln_2.copy_(ml.ln_2.weight); b.c_fc.copy_(ml.c_fc.weight); b.c_proj2.copy_(ml.c_proj.weight)
     loss_ours = ours(idx, tgt)
     assert abs(float(loss_ours) - float(loss)) < 2e-2 * float(loss)   # fp16 vs bf16 LM head, otherwise the same operators
+    # ... and the same gradients: the reference's autograd Functions and this package's harness wire the backward operators
+    # the same way (different stochastic-rounding draws, so cosine and norm instead of bits)
+    loss_ours.backward()
+    pairs = [("wte", ours.wte.weight, model.transformer.wte.weight), ("wpe", ours.wpe.weight, model.transformer.wpe.weight),
+             ("ln_f", ours.ln_f, model.transformer.ln_f.weight)]
+    for i, (b, rb) in enumerate(zip(ours.blocks, model.transformer.h)):
+        at, ml = rb.attn_residual, rb.mlp_residual
+        pairs += [(f"h{i}.ln_1", b.ln_1, at.ln_1.weight), (f"h{i}.c_attn", b.c_attn, at.c_attn.weight), (f"h{i}.c_proj", b.c_proj, at.c_proj.weight),
+                  (f"h{i}.ln_2", b.ln_2, ml.ln_2.weight), (f"h{i}.c_fc", b.c_fc, ml.c_fc.weight), (f"h{i}.c_proj2", b.c_proj2, ml.c_proj.weight)]
+    worst = (2.0, 1.0, "")
+    for name, po, pr in pairs:
+        a, r = po.grad.flatten().float(), pr.grad.flatten().float()
+        cos, ratio = float(torch.dot(a, r) / (a.norm() * r.norm())), float(a.norm() / r.norm())
+        worst = min(worst, (cos, ratio, name))
+        assert cos > 0.98 and 0.9 < ratio < 1.1, (name, cos, ratio)
+    print(f"gradients of this package's harness vs the reference's qmodel.py on the same operators: lowest cosine {worst[0]:.4f} ({worst[2]})")
 
 
 @needs_ref
