@@ -11,7 +11,8 @@ kernels recompiled for Blackwell's legacy tensor path.  They serve two purposes,
   * the GPU-side baseline timing of `bench.py --impl reference --workload gemm_sweep`.
 `load_nonlinear()` imports the reference's Triton operators (Jetfire/Nonlinear/*.py, nothing to build) for the same two uses:
 tests/test_gpu_reference_triton.py and `bench.py --impl reference --workload nonlinear`.
-The checkout is found through --reference, $JETFIRE_REFERENCE, or /root/reference; without one this script does nothing.
+The checkout is found through --reference, $JETFIRE_REFERENCE, or the default location DEFAULT_REFERENCE; without one this script
+does nothing.
 """
 import os
 import subprocess
@@ -21,6 +22,7 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "BlockQuantizeCUDA.so")
+DEFAULT_REFERENCE = "/root/reference"
 
 SOURCES = [
     "igemm/igemm_BlockSquare32OutputIntQuantizeStochastic.cu",
@@ -36,7 +38,7 @@ SOURCES = [
 
 
 def reference_root(arg=None):
-    for cand in (arg, os.environ.get("JETFIRE_REFERENCE"), "/root/reference"):
+    for cand in (arg, os.environ.get("JETFIRE_REFERENCE"), DEFAULT_REFERENCE):
         if cand and os.path.isdir(os.path.join(cand, "JetfireGEMMKernel", "BlockQuantize", "cpp_extension")):
             return cand
     return None
@@ -99,10 +101,10 @@ def load():
 
 
 def nonlinear_root():
-    """Directory holding the reference's Jetfire/Nonlinear/*.py: a checkout ($JETFIRE_REFERENCE, /root/reference) or the copies
+    """Directory holding the reference's Jetfire/Nonlinear/*.py: a checkout ($JETFIRE_REFERENCE, DEFAULT_REFERENCE) or the copies
     that tests/stage_reference.py staged into baseline/_ref/ (git-ignored) so that they exist on a GPU box."""
     staged = os.path.join(os.path.dirname(HERE), "baseline", "_ref")
-    for cand in (os.environ.get("JETFIRE_REFERENCE"), "/root/reference", staged):
+    for cand in (os.environ.get("JETFIRE_REFERENCE"), DEFAULT_REFERENCE, staged):
         if cand and os.path.exists(os.path.join(cand, "Jetfire", "Nonlinear", "layernorm.py")):
             return cand
     return None

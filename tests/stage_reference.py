@@ -15,6 +15,7 @@ import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 STAGE = os.path.join(ROOT, "baseline", "_ref")
+DEFAULT_REFERENCE = "/root/reference"
 FILES = ["INT8_GPT2/qmodel.py", "Jetfire/Linear/__init__.py", "Jetfire/Linear/linear_fwd.py", "Jetfire/Linear/linear_bwd.py"]
 FILES += [f"Jetfire/Nonlinear/{m}.py" for m in ("__init__", "add", "add_mean_var", "common", "dequantize", "gelu_bwd", "gelu_fwd",
                                                 "layernorm", "quantize", "quantize_transpose", "transpose", "utils")]
@@ -22,14 +23,14 @@ FILES += [f"Jetfire/Nonlinear/{m}.py" for m in ("__init__", "add", "add_mean_var
 
 def reference_files_root():
     """Directory that holds the reference files: an actual checkout if one is reachable, else the staged copies, else None."""
-    for cand in (os.environ.get("JETFIRE_REFERENCE"), "/root/reference", STAGE):
+    for cand in (os.environ.get("JETFIRE_REFERENCE"), DEFAULT_REFERENCE, STAGE):
         if cand and all(os.path.exists(os.path.join(cand, f)) for f in FILES):
             return cand
     return None
 
 
 def stage(reference=None):
-    src = reference or os.environ.get("JETFIRE_REFERENCE") or "/root/reference"
+    src = reference or os.environ.get("JETFIRE_REFERENCE") or DEFAULT_REFERENCE
     if not all(os.path.exists(os.path.join(src, f)) for f in FILES):
         raise SystemExit(f"no reference checkout at {src}")
     for f in FILES:

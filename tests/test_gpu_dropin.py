@@ -6,7 +6,7 @@
     this package's `BlockQuantizeCUDA` shim: transposed scale copies, the `W8.t()` view, the materialised dY^T with
     g_transposed = 1 -- results bit for bit against the CPU oracle.
 
-The reference files come from $JETFIRE_REFERENCE, a checkout at /root/reference, or the copies staged by
+The reference files come from $JETFIRE_REFERENCE, a checkout at the default location, or the copies staged by
 tests/stage_reference.py; without any of them the tests skip.
 """
 import importlib.util
