@@ -114,3 +114,30 @@ def test_clip_adamw_refuses_cpu_parameters():
     from jetfire_int8training_b200.optim import ClipAdamW
     with pytest.raises(ValueError):
         ClipAdamW([([torch.nn.Parameter(torch.zeros(8))], 0.0)], lr=1e-3)
+
+
+def test_argument_validation_of_the_newer_entry_points(libpath):
+    """jf_int8_quantize_multi, jf_lm_loss_* and jf_adamw_clip_step refuse bad arguments before touching a device."""
+    from jetfire_int8training_b200 import _lib
+    L = _lib.lib()
+    buf = (ctypes.c_char * 4096)()
+    p = (ctypes.addressof(buf) + 15) & ~15
+    one = ctypes.c_void_p * 1
+    i64 = ctypes.c_int64 * 1
+    f32 = ctypes.c_float * 1
+    assert L.jf_int8_quantize_multi(0, one(p), 0, i64(32), i64(32), one(p), one(p), None) == -7          # count out of 1..8
+    assert L.jf_int8_quantize_multi(9, one(p), 0, i64(32), i64(32), one(p), one(p), None) == -7
+    assert L.jf_int8_quantize_multi(1, one(p), 0, i64(33), i64(32), one(p), one(p), None) == -2          # not a multiple of 32
+    assert L.jf_int8_quantize_multi(1, one(None), 0, i64(32), i64(32), one(p), one(p), None) == -1
+    assert L.jf_lm_loss_forward(None, p, 4, 512, p, p, None) == -1
+    assert L.jf_lm_loss_forward(p, p, 0, 512, p, p, None) == -2
+    assert L.jf_adamw_chunk_elements() == 4096
+    args = dict(lr=1e-3, b1=0.9, b2=0.95, eps=1e-8, mn=1.0)
+    call = lambda n, g, numel, start, total, state=p: L.jf_adamw_clip_step(n, g, numel, start, f32(0.0), p, p, p, total, 1e-3, 0.9, 0.95,
+                                                                            1e-8, 1.0, state, 2000, 2.0, 0.5, p, None)
+    assert call(1, one(p), i64(4096), i64(0), 1, state=None) == -1
+    assert call(0, one(p), i64(4096), i64(0), 1) == -2
+    assert call(1, one(p), i64(4098), i64(0), 2) == -2                      # numel not a multiple of 4
+    assert call(1, one(p), i64(8192), i64(0), 1) == -2                      # the segment does not fit its chunks
+    assert call(1, one(p + 4), i64(4096), i64(0), 1) == -3                  # gradient not 16-byte aligned
+    assert call(1, one(None), i64(4096), i64(0), 1) == -1
